@@ -1,0 +1,14 @@
+"""fast_route_b200: the fused-routing Mixture-of-Experts layer of hgl71964/fast-route,
+rebuilt for NVIDIA B200 (sm_100a) as hand-written CUDA behind a C ABI.
+
+``ops`` and ``layers`` mirror the reference's ``fast_route.ops`` / ``fast_route.layers``
+operator surface; ``parallel`` adds expert parallelism over NCCL.
+"""
+
+from . import _lib
+from .layers.stable_route import fused_moe
+from .ops.stable_route import fused_route, route_from_logits
+from .ops.fused_moe import moe_align_block_size, invoke_fused_moe_kernel
+
+__all__ = ["fused_moe", "fused_route", "route_from_logits", "moe_align_block_size",
+           "invoke_fused_moe_kernel", "_lib"]

@@ -1,0 +1,443 @@
+// C ABI of libfastroute_sm100.so: argument checks, workspace carving, the memory-bound
+// helper kernels (row permute / gather, combine, gate transpose) and the whole-layer
+// launch sequence.  See include/fast_route_sm100.h for the contract of every entry point.
+#include "fr_common.cuh"
+
+namespace fr {
+
+int topk_softmax_dispatch(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e,
+                          int k, int renormalize, float* weights, int64_t w_stride, int32_t* ids,
+                          int64_t id_stride, int fill_rest, cudaStream_t st);
+int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
+                   int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
+                   int32_t* inv_pos, cudaStream_t st);
+int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, int dtype, int64_t max_rows,
+                          int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
+                          const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
+                          void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
+                          cudaStream_t st);
+int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate_km,
+                         int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
+                         int32_t* ids, float* logits_out, cudaStream_t st);
+int choose_split_k(int64_t est_tiles, int KB, int sm_count);
+
+constexpr int kBlockM = FR_GEMM_BLOCK_M;
+constexpr int kTileN = 256;
+constexpr int kTileK = 64;
+
+// ----------------------------------------------------------------------------------
+// memory-bound helpers
+// ----------------------------------------------------------------------------------
+// dst[p,:] = src[sorted_ids[p] / topk, :] for p < num_post; padding entries become zeros.
+__global__ void __launch_bounds__(256) permute_rows_kernel(const uint4* __restrict__ src, int64_t ld_src_v,
+                                                           const int32_t* __restrict__ sorted_ids,
+                                                           const int32_t* __restrict__ num_post, int64_t n, int topk,
+                                                           uint4* __restrict__ dst, int64_t ld_dst_v, int row_v) {
+  const int64_t row = blockIdx.x;
+  if (num_post && row >= __ldg(num_post)) return;
+  const int32_t sid = __ldg(sorted_ids + row);
+  uint4* d = dst + row * ld_dst_v;
+  if (sid >= 0 && sid < n) {
+    const uint4* s = src + static_cast<int64_t>(sid / topk) * ld_src_v;
+    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = __ldg(s + v);
+  } else {
+    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// dst[i,:] = src[idx[i],:]; idx < 0 -> zeros
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restrict__ src, int64_t ld_src_v,
+                                                          const int32_t* __restrict__ idx, uint4* __restrict__ dst,
+                                                          int64_t ld_dst_v, int row_v) {
+  const int64_t row = blockIdx.x;
+  const int32_t s = __ldg(idx + row);
+  uint4* d = dst + row * ld_dst_v;
+  if (s >= 0) {
+    const uint4* sp = src + static_cast<int64_t>(s) * ld_src_v;
+    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = __ldg(sp + v);
+  } else {
+    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// out[t,:] = sum_j y[inv_pos[t*topk+j], :], fp32 accumulation in slot order, one rounding.
+template <bool BF16>
+__global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ y, int64_t ld_y_v,
+                                                      const int32_t* __restrict__ inv_pos, int topk, int row_v,
+                                                      int64_t max_rows, uint4* __restrict__ out, int64_t ld_out_v) {
+  const int64_t t = blockIdx.x;
+  for (int v = threadIdx.x; v < row_v; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (int j = 0; j < topk; ++j) {
+      const int32_t pos = __ldg(inv_pos + t * topk + j);
+      if (pos < 0 || pos >= max_rows) continue;
+      const uint4 raw = __ldg(y + static_cast<int64_t>(pos) * ld_y_v + v);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<BF16>(w[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    out[t * ld_out_v + v] = make_uint4(pack2<BF16>(acc[0], acc[1]), pack2<BF16>(acc[2], acc[3]),
+                                       pack2<BF16>(acc[4], acc[5]), pack2<BF16>(acc[6], acc[7]));
+  }
+}
+
+// gate[h*sh + e*se] (two-byte elements) -> gate_km[e*ld + h]
+__global__ void transpose_gate_kernel(const uint16_t* __restrict__ gate, int64_t sh, int64_t se, int H, int E,
+                                      uint16_t* __restrict__ out, int64_t ld) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (i >= static_cast<int64_t>(E) * ld) return;
+  const int e = static_cast<int>(i / ld);
+  const int h = static_cast<int>(i % ld);
+  out[i] = h < H ? gate[h * sh + e * se] : static_cast<uint16_t>(0);
+}
+
+// ----------------------------------------------------------------------------------
+// workspace carving
+// ----------------------------------------------------------------------------------
+struct Carver {
+  uint8_t* base;
+  size_t off = 0;
+  explicit Carver(void* b) : base(static_cast<uint8_t*>(b)) {}
+  template <typename T>
+  T* take(size_t count) {
+    off = (off + 1023) & ~size_t(1023);
+    T* p = base ? reinterpret_cast<T*>(base + off) : nullptr;
+    off += count * sizeof(T);
+    return p;
+  }
+  size_t total() const { return (off + 1023) & ~size_t(1023); }
+};
+
+static int64_t round_up(int64_t a, int64_t b) { return (a + b - 1) / b * b; }
+
+static int sm_count_or_default() {
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess &&
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && sms > 0)
+    return sms;
+  (void)cudaGetLastError();
+  return 148;
+}
+
+// Upper bound on padded rows: every expert that can hold a token pads by < kBlockM.
+static int64_t rows_cap(int64_t n, int E) {
+  const int64_t active = n < E ? n : E;
+  return round_up(n + active * (kBlockM - 1), kBlockM);
+}
+
+struct SplitPlan {
+  int s1 = 1, s2 = 1;
+  size_t bytes = 0;
+};
+static SplitPlan plan_split(int64_t n, int H, int I, int E) {
+  SplitPlan sp;
+  if (n <= 0) return sp;
+  const int sms = sm_count_or_default();
+  const int64_t est_mb = (n < E ? n : E) + n / kBlockM;
+  const int nb1 = (I + kTileN / 2 - 1) / (kTileN / 2), nb2 = (H + kTileN - 1) / kTileN;
+  sp.s1 = choose_split_k(est_mb * nb1, (H + kTileK - 1) / kTileK, sms);
+  sp.s2 = choose_split_k(est_mb * nb2, (I + kTileK - 1) / kTileK, sms);
+  size_t b1 = sp.s1 > 1 ? static_cast<size_t>(sp.s1) * n * nb1 * kTileN * sizeof(float) : 0;
+  size_t b2 = sp.s2 > 1 ? static_cast<size_t>(sp.s2) * n * nb2 * kTileN * sizeof(float) : 0;
+  sp.bytes = b1 > b2 ? b1 : b2;
+  return sp;
+}
+
+struct RouteWs {
+  uint16_t* gate_km;
+  float* logits;
+  int64_t ld_gate;
+};
+static RouteWs carve_route(Carver& c, int64_t M, int H, int E, int topk) {
+  RouteWs r;
+  r.ld_gate = round_up(H, 8);
+  r.gate_km = c.take<uint16_t>(static_cast<size_t>(E) * r.ld_gate);
+  const bool need_logits = topk > 8;
+  r.logits = c.take<float>(need_logits ? static_cast<size_t>(M) * E : 0);
+  return r;
+}
+
+static int route_fused_impl(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate,
+                            int64_t gsh, int64_t gse, int E, int topk, int renormalize, float* weights,
+                            int32_t* ids, float* logits_out, const RouteWs& ws, cudaStream_t st) {
+  const void* gate_km = gate;
+  int64_t ld_gate = gse;
+  if (gsh != 1 || (gse % 8) != 0 || (reinterpret_cast<uintptr_t>(gate) & 15)) {
+    const int64_t total = static_cast<int64_t>(E) * ws.ld_gate;
+    transpose_gate_kernel<<<static_cast<unsigned>((total + 255) / 256), 256, 0, st>>>(
+        static_cast<const uint16_t*>(gate), gsh, gse, H, E, ws.gate_km, ws.ld_gate);
+    FR_CUDA_OK(cudaGetLastError());
+    gate_km = ws.gate_km;
+    ld_gate = ws.ld_gate;
+  }
+  if (topk <= 8) {
+    return router_gemm_dispatch(x, dtype, M, H, ldx, gate_km, ld_gate, E, topk, renormalize, 1, weights, ids,
+                                logits_out, st);
+  }
+  float* lg = logits_out ? logits_out : ws.logits;
+  int rc = router_gemm_dispatch(x, dtype, M, H, ldx, gate_km, ld_gate, E, topk, renormalize, 0, nullptr, nullptr,
+                                lg, st);
+  if (rc) return rc;
+  return topk_softmax_dispatch(lg, FR_F32, M, E, E, 1, topk, renormalize, weights, topk, ids, topk, 0, st);
+}
+
+struct ExpertWs {
+  int32_t *sorted, *expert_ids, *num_post, *inv_pos;
+  uint16_t *a_sorted, *act, *y_sorted;
+  void* split;
+  int64_t rows, sorted_len, expert_ids_len;
+  SplitPlan sp;
+};
+static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
+  ExpertWs w;
+  w.rows = rows_cap(n, E);
+  w.sorted_len = round_up(n + static_cast<int64_t>(E) * (kBlockM - 1), kBlockM);
+  w.expert_ids_len = w.sorted_len / kBlockM + 1;
+  w.sorted = c.take<int32_t>(w.sorted_len);
+  w.expert_ids = c.take<int32_t>(w.expert_ids_len);
+  w.num_post = c.take<int32_t>(4);
+  w.inv_pos = c.take<int32_t>(n);
+  w.a_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
+  w.act = c.take<uint16_t>(static_cast<size_t>(w.rows) * I);
+  w.y_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
+  w.sp = plan_split(n, H, I, E);
+  w.split = c.take<uint8_t>(w.sp.bytes);
+  return w;
+}
+
+// align -> permute -> GEMM1+SiLU -> GEMM2 -> combine for n assignments (flat id i belongs to
+// token i / topk) whose expert ids are in `ids`.
+static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const float* weights, const void* w1,
+                        const void* w2, int dtype, int64_t M, int topk, int H, int I, int E, void* out,
+                        int64_t ld_out, const ExpertWs& w, cudaStream_t st) {
+  const int64_t n = M * topk;
+  int rc = align_dispatch(ids, n, E, kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len, w.num_post,
+                          nullptr, w.inv_pos, st);
+  if (rc) return rc;
+  const int row_v = H / 8;
+  permute_rows_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
+      static_cast<const uint4*>(x), ldx / 8, w.sorted, w.num_post, n, topk, reinterpret_cast<uint4*>(w.a_sorted),
+      H / 8, row_v);
+  FR_CUDA_OK(cudaGetLastError());
+  rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
+                             w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st);
+  if (rc) return rc;
+  rc = gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
+                             weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st);
+  if (rc) return rc;
+  if (dtype == FR_BF16)
+    combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
+        reinterpret_cast<const uint4*>(w.y_sorted), H / 8, w.inv_pos, topk, row_v, w.rows,
+        static_cast<uint4*>(out), ld_out / 8);
+  else
+    combine_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(
+        reinterpret_cast<const uint4*>(w.y_sorted), H / 8, w.inv_pos, topk, row_v, w.rows,
+        static_cast<uint4*>(out), ld_out / 8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace fr
+
+using namespace fr;
+
+extern "C" {
+
+int fr_version(void) { return 100; }
+
+const char* fr_error_string(int code) {
+  switch (code) {
+    case FR_OK: return "ok";
+    case FR_ERR_ARG: return "invalid argument";
+    case FR_ERR_UNSUPPORTED: return "size, dtype or layout not supported";
+    case FR_ERR_ALIGN: return "pointer or stride not 16-byte aligned";
+    case FR_ERR_WORKSPACE: return "workspace missing or too small";
+    case FR_ERR_DRIVER: return "CUDA driver tensor-map entry point unavailable or rejected the descriptor";
+    default: return code > 0 ? cudaGetErrorString(static_cast<cudaError_t>(code)) : "unknown error";
+  }
+}
+
+int fr_check_status(unsigned int* out4) {
+  if (!out4) return FR_ERR_ARG;
+  FR_CUDA_OK(cudaDeviceSynchronize());
+  FR_CUDA_OK(cudaMemcpyFromSymbol(out4, g_status, 4 * sizeof(unsigned int)));
+  const unsigned int zero[4] = {0, 0, 0, 0};
+  FR_CUDA_OK(cudaMemcpyToSymbol(g_status, zero, sizeof(zero)));
+  return FR_OK;
+}
+
+int fr_topk_softmax(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e, int topk,
+                    int renormalize, float* weights, int64_t w_stride, int32_t* ids, int64_t id_stride,
+                    int fill_rest, void* stream) {
+  return topk_softmax_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, renormalize, weights, w_stride, ids,
+                               id_stride, fill_rest, static_cast<cudaStream_t>(stream));
+}
+
+int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids, int64_t sorted_len,
+             int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad, int32_t* counts,
+             int32_t* inv_pos, void* stream) {
+  return align_dispatch(topk_ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
+                        num_tokens_post_pad, counts, inv_pos, static_cast<cudaStream_t>(stream));
+}
+
+int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e, int topk,
+                   float* weights, int32_t* ids, int block_size, int32_t* sorted_ids, int64_t sorted_len,
+                   int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad, void* stream) {
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = topk_softmax_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, 1, weights, topk, ids, topk, 0, st);
+  if (rc) return rc;
+  return align_dispatch(ids, M * topk, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
+                        num_tokens_post_pad, nullptr, nullptr, st);
+}
+
+size_t fr_route_fused_workspace_bytes(int64_t M, int H, int E, int topk) {
+  Carver c(nullptr);
+  carve_route(c, M, H, E, topk);
+  return c.total();
+}
+
+int fr_route_fused(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate, int64_t gate_stride_h,
+                   int64_t gate_stride_e, int E, int topk, int renormalize, float* weights, int32_t* ids,
+                   float* logits_out, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !gate || !weights || !ids || M < 0 || H <= 0 || E <= 0 || topk <= 0 || topk > E) return FR_ERR_ARG;
+  if (M == 0) return FR_OK;
+  if (!workspace || workspace_bytes < fr_route_fused_workspace_bytes(M, H, E, topk)) return FR_ERR_WORKSPACE;
+  Carver c(workspace);
+  RouteWs ws = carve_route(c, M, H, E, topk);
+  return route_fused_impl(x, dtype, M, H, ldx, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, weights,
+                          ids, logits_out, ws, static_cast<cudaStream_t>(stream));
+}
+
+int fr_permute_rows(const void* src, int dtype, int H, int64_t ld_src, const int32_t* sorted_ids,
+                    const int32_t* num_tokens_post_pad, int64_t n, int topk, int64_t max_rows, void* dst,
+                    int64_t ld_dst, void* stream) {
+  if (!src || !sorted_ids || !dst || H <= 0 || topk <= 0 || max_rows < 0) return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (ld_src % 8) || (ld_dst % 8) || (reinterpret_cast<uintptr_t>(src) & 15) ||
+      (reinterpret_cast<uintptr_t>(dst) & 15))
+    return FR_ERR_ALIGN;
+  if (max_rows == 0) return FR_OK;
+  permute_rows_kernel<<<static_cast<unsigned>(max_rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), ld_src / 8, sorted_ids, num_tokens_post_pad, n, topk,
+      static_cast<uint4*>(dst), ld_dst / 8, H / 8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int fr_gather_rows(const void* src, int64_t ld_src, const int32_t* idx, int64_t rows, int row_bytes, void* dst,
+                   int64_t ld_dst, void* stream) {
+  if (!src || !idx || !dst || rows < 0 || row_bytes <= 0) return FR_ERR_ARG;
+  if ((row_bytes % 16) || (ld_src % 16) || (ld_dst % 16) || (reinterpret_cast<uintptr_t>(src) & 15) ||
+      (reinterpret_cast<uintptr_t>(dst) & 15))
+    return FR_ERR_ALIGN;
+  if (rows == 0) return FR_OK;
+  gather_rows_kernel<<<static_cast<unsigned>(rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), ld_src / 16, idx, static_cast<uint4*>(dst), ld_dst / 16, row_bytes / 16);
+  return static_cast<int>(cudaGetLastError());
+}
+
+size_t fr_gemm_splitk_workspace_bytes(int64_t n_valid, int64_t n_cols, int split_k) {
+  if (split_k <= 1) return 0;
+  return static_cast<size_t>(split_k) * static_cast<size_t>(n_valid) * round_up(n_cols, kTileN) * sizeof(float);
+}
+
+int fr_gemm1_silu(const void* a_sorted, int64_t lda, const void* w1, int dtype, int64_t max_rows, int H, int I,
+                  int E, const int32_t* expert_ids, const int32_t* num_tokens_post_pad, const int32_t* sorted_ids,
+                  int64_t n, void* act, int64_t ld_act, int split_k, void* workspace, size_t workspace_bytes,
+                  void* stream) {
+  return gemm_grouped_dispatch(0, a_sorted, lda, w1, dtype, max_rows, H, I, E, 2 * I, expert_ids,
+                               num_tokens_post_pad, sorted_ids, nullptr, n, act, ld_act, split_k, workspace,
+                               workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int fr_gemm2(const void* act, int64_t ld_act, const void* w2, int dtype, int64_t max_rows, int H, int I, int E,
+             const int32_t* expert_ids, const int32_t* num_tokens_post_pad, const int32_t* sorted_ids,
+             const float* topk_weights, int64_t n, void* y, int64_t ld_y, int split_k, void* workspace,
+             size_t workspace_bytes, void* stream) {
+  return gemm_grouped_dispatch(1, act, ld_act, w2, dtype, max_rows, I, H, E, H, expert_ids, num_tokens_post_pad,
+                               sorted_ids, topk_weights, n, y, ld_y, split_k, workspace, workspace_bytes,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int fr_combine(const void* y, int64_t ld_y, int dtype, const int32_t* inv_pos, int64_t M, int topk, int H,
+               int64_t max_rows, void* out, int64_t ld_out, void* stream) {
+  if (!y || !inv_pos || !out || M < 0 || topk <= 0 || H <= 0) return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (ld_y % 8) || (ld_out % 8) || (reinterpret_cast<uintptr_t>(y) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return FR_ERR_ALIGN;
+  if (M == 0) return FR_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FR_BF16)
+    combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(static_cast<const uint4*>(y), ld_y / 8, inv_pos,
+                                                                   topk, H / 8, max_rows, static_cast<uint4*>(out),
+                                                                   ld_out / 8);
+  else
+    combine_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(static_cast<const uint4*>(y), ld_y / 8, inv_pos,
+                                                                    topk, H / 8, max_rows, static_cast<uint4*>(out),
+                                                                    ld_out / 8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+size_t fr_moe_workspace_bytes(int64_t M, int H, int I, int E, int topk) {
+  if (M <= 0 || H <= 0 || I <= 0 || E <= 0 || topk <= 0) return 0;
+  Carver c(nullptr);
+  carve_route(c, M, H, E, topk);
+  c.take<float>(M * topk);
+  c.take<int32_t>(M * topk);
+  carve_experts(c, M * topk, H, I, E);
+  return c.total();
+}
+
+int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t gate_stride_e, const void* w1,
+                 const void* w2, int dtype, int64_t M, int H, int I, int E, int topk, int renormalize, void* out,
+                 float* topk_weights_out, int32_t* topk_ids_out, void* workspace, size_t workspace_bytes,
+                 void* stream) {
+  if (!x || !gate || !w1 || !w2 || !out || M < 0 || H <= 0 || I <= 0 || E <= 0 || topk <= 0 || topk > E)
+    return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (I % 8)) return FR_ERR_ALIGN;
+  if (M == 0) return FR_OK;
+  if (!workspace || workspace_bytes < fr_moe_workspace_bytes(M, H, I, E, topk)) return FR_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Carver c(workspace);
+  RouteWs rws = carve_route(c, M, H, E, topk);
+  float* tw = c.take<float>(M * topk);
+  int32_t* ti = c.take<int32_t>(M * topk);
+  ExpertWs ews = carve_experts(c, M * topk, H, I, E);
+  if (topk_weights_out) tw = topk_weights_out;
+  if (topk_ids_out) ti = topk_ids_out;
+  int rc = route_fused_impl(x, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
+                            nullptr, rws, st);
+  if (rc) return rc;
+  return experts_impl(x, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st);
+}
+
+size_t fr_moe_experts_workspace_bytes(int64_t R, int H, int I, int E_local) {
+  if (R <= 0 || H <= 0 || I <= 0 || E_local <= 0) return 0;
+  Carver c(nullptr);
+  carve_experts(c, R, H, I, E_local);
+  return c.total();
+}
+
+int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row_weight, const void* w1,
+                   const void* w2, int dtype, int64_t R, int H, int I, int E_local, void* y, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+  if (!rows || !row_expert || !w1 || !w2 || !y || R < 0 || H <= 0 || I <= 0 || E_local <= 0) return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (I % 8)) return FR_ERR_ALIGN;
+  if (R == 0) return FR_OK;
+  if (!workspace || workspace_bytes < fr_moe_experts_workspace_bytes(R, H, I, E_local)) return FR_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
+  Carver c(workspace);
+  ExpertWs ews = carve_experts(c, R, H, I, E_local);
+  return experts_impl(rows, H, row_expert, row_weight, w1, w2, dtype, R, 1, H, I, E_local, y, H, ews,
+                      static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,5 @@
+from .stable_route import fused_route, route_from_logits
+from .fused_moe import moe_align_block_size, invoke_fused_moe_kernel, gemm1_silu, gemm2, permute_rows, combine
+
+__all__ = ["fused_route", "route_from_logits", "moe_align_block_size", "invoke_fused_moe_kernel",
+           "gemm1_silu", "gemm2", "permute_rows", "combine"]

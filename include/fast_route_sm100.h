@@ -1,0 +1,162 @@
+/*
+ * fast_route_sm100.h - C ABI of libfastroute_sm100.so, the sm_100a (B200) implementation of
+ * the fused-routing Mixture-of-Experts layer.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream (passed as void*,
+ * the value of a cudaStream_t), launches asynchronously on that stream, allocates nothing
+ * and keeps no pointer after it returns.  Return value: 0 = ok, negative = argument
+ * rejected on the host (see fr_error_string), positive = a cudaError_t.
+ * Device-side problems (an id out of range, a bounded wait that expired) never trap: they
+ * are recorded in a device status block read with fr_check_status().
+ *
+ * Each declaration names the interface of the reference (hgl71964/fast-route, paths inside
+ * that project) that it stands in for.
+ */
+#ifndef FAST_ROUTE_SM100_H_
+#define FAST_ROUTE_SM100_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* element types of activations / weights / logits */
+enum { FR_F16 = 0, FR_BF16 = 1, FR_F32 = 2 };
+
+/* host-side argument errors */
+enum {
+  FR_OK = 0,
+  FR_ERR_ARG = -1,         /* null pointer, negative size, k > E ... */
+  FR_ERR_UNSUPPORTED = -2, /* a size or layout outside what the kernels cover */
+  FR_ERR_ALIGN = -3,       /* pointer or stride not 16-byte aligned where TMA needs it */
+  FR_ERR_WORKSPACE = -4,   /* workspace too small */
+  FR_ERR_DRIVER = -5       /* the CUDA driver entry point for tensor maps is unavailable */
+};
+
+/* alignment block of the expert GEMMs: the reference passes its Triton BLOCK_SIZE_M
+ * (fast_route/fast_route/layers/stable_route.py:82-83); here it is the MMA tile height. */
+#define FR_GEMM_BLOCK_M 128
+
+int fr_version(void);
+const char* fr_error_string(int code);
+
+/* Synchronous read (and clear) of the device status block of the current device:
+ * out4[0] = first error code (0 ok, 1 wait timeout, 2 expert id out of range,
+ * 3 bad sorted id), out4[1] = detail, out4[2] = block, out4[3] = count.
+ * No counterpart in the reference, whose kernels have no error reporting. */
+int fr_check_status(unsigned int* out4);
+
+/* Router from logits: stable descending top-k (ties -> lower expert id) and softmax over
+ * the selected k.  Stands in for the epilogue of route_kernel,
+ * fast_route/fast_route/ops/stable_route.py:91-121, and for stable_argsort,
+ * ops/stable_argsort.py:96-114.  logits[M,E] with element strides; weights fp32 and ids
+ * int32 are written at [row*stride + j].  fill_rest != 0 reproduces what the reference
+ * leaves in [M,E] buffers (ids: the full argsort; weights: zeros past k).
+ * renormalize == 0 divides by the sum over all E columns instead. */
+int fr_topk_softmax(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e,
+                    int topk, int renormalize, float* weights, int64_t w_stride, int32_t* ids,
+                    int64_t id_stride, int fill_rest, void* stream);
+
+/* Stable counting sort of the n = M*topk flattened routing ids by expert, every expert's
+ * segment padded to a multiple of block_size with the sentinel n.  Stands in for
+ * moe_align_block_size, fast_route/fast_route/ops/fused_moe.py:133-175 (the vLLM 0.4.0 CUDA
+ * op it calls plus the fill_ of the wrapper).  sorted_ids has sorted_len entries
+ * (>= n + E*(block_size-1)), expert_ids has expert_ids_len entries; entries past the valid
+ * prefix are set to n / -1.  Optional outputs (may be NULL): counts[E] tokens per expert,
+ * inv_pos[n] position of every flat assignment in sorted_ids. */
+int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids,
+             int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad,
+             int32_t* counts, int32_t* inv_pos, void* stream);
+
+/* fr_topk_softmax followed by fr_align on its compact [M,topk] ids: the routing/align
+ * latency path (logits -> the five routing outputs). */
+int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e,
+                   int topk, float* weights, int32_t* ids, int block_size, int32_t* sorted_ids,
+                   int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len,
+                   int32_t* num_tokens_post_pad, void* stream);
+
+/* Fused router: logits = X[M,H] . G[H,E] on the tensor cores with the top-k / softmax
+ * epilogue in registers.  Stands in for fused_route + route_kernel,
+ * fast_route/fast_route/ops/stable_route.py:32-178.  x is row-major with row pitch ldx
+ * elements; gate element (h,e) is at gate[h*gate_stride_h + e*gate_stride_e] (the layer
+ * passes W_g[E,H].t(), i.e. gate_stride_h = 1; a row-major [H,E] gate is transposed into
+ * the workspace first).  weights/ids are compact [M,topk].  logits_out (may be NULL)
+ * receives the fp32 logits [M,E].  dtype is FR_F16 or FR_BF16. */
+size_t fr_route_fused_workspace_bytes(int64_t M, int H, int E, int topk);
+int fr_route_fused(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate,
+                   int64_t gate_stride_h, int64_t gate_stride_e, int E, int topk, int renormalize,
+                   float* weights, int32_t* ids, float* logits_out, void* workspace, size_t workspace_bytes,
+                   void* stream);
+
+/* Gathers token rows into expert-sorted order: dst[p,:] = src[sorted_ids[p] / topk, :] for
+ * p < num_tokens_post_pad (zeros for padding entries).  Stands in for the gathered A loads
+ * of fused_moe_kernel, fast_route/fast_route/ops/fused_moe.py:82-89. */
+int fr_permute_rows(const void* src, int dtype, int H, int64_t ld_src, const int32_t* sorted_ids,
+                    const int32_t* num_tokens_post_pad, int64_t n, int topk, int64_t max_rows, void* dst,
+                    int64_t ld_dst, void* stream);
+
+/* Grouped expert GEMM 1 with the SiLU-and-multiply epilogue, on expert-sorted rows:
+ * act[p, j] = silu(a[p,:] . w1[e, j, :]) * (a[p,:] . w1[e, I + j, :]),  e = expert_ids[p / 128].
+ * Stands in for invoke_fused_moe_kernel(..., mul_routed_weight=False)
+ * (fast_route/fast_route/ops/fused_moe.py:10-130, 178-214) followed by ops.silu_and_mul
+ * (fast_route/fast_route/layers/stable_route.py:85-90).  a_sorted[max_rows, H] (pitch lda),
+ * w1[E, 2I, H] contiguous, act[max_rows, I] (pitch ld_act), max_rows a multiple of 128.
+ * split_k > 1 (few rows, many K slices: the small-batch path) sums fp32 partial tiles in
+ * slice order; it needs sorted_ids, the number n of real assignments and a workspace of
+ * fr_gemm_splitk_workspace_bytes(n, 2*I, split_k) bytes.  sorted_ids may be NULL otherwise. */
+size_t fr_gemm_splitk_workspace_bytes(int64_t n, int64_t n_cols, int split_k);
+int fr_gemm1_silu(const void* a_sorted, int64_t lda, const void* w1, int dtype, int64_t max_rows, int H, int I,
+                  int E, const int32_t* expert_ids, const int32_t* num_tokens_post_pad, const int32_t* sorted_ids,
+                  int64_t n, void* act, int64_t ld_act, int split_k, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/* Grouped expert GEMM 2 with the routed weight applied in fp32 before rounding:
+ * y[p, h] = topk_weights[sorted_ids[p]] * (act[p,:] . w2[e, h, :]).
+ * Stands in for invoke_fused_moe_kernel(..., mul_routed_weight=True, top_k=1)
+ * (fast_route/fast_route/ops/fused_moe.py:117-121, layers/stable_route.py:92-95).
+ * Output rows stay in expert-sorted order; fr_combine gathers them per token.
+ * topk_weights (flat [n], indexed by sorted id) may be NULL (weight 1).  split_k as above
+ * with fr_gemm_splitk_workspace_bytes(n, H, split_k). */
+int fr_gemm2(const void* act, int64_t ld_act, const void* w2, int dtype, int64_t max_rows, int H, int I, int E,
+             const int32_t* expert_ids, const int32_t* num_tokens_post_pad, const int32_t* sorted_ids,
+             const float* topk_weights, int64_t n, void* y, int64_t ld_y, int split_k, void* workspace,
+             size_t workspace_bytes, void* stream);
+
+/* Combine: out[t,:] = sum_j y[inv_pos[t*topk + j], :], accumulated in fp32 in slot order and
+ * rounded once; positions outside [0, max_rows) are skipped.
+ * Stands in for torch.sum(intermediate_cache3, dim=1),
+ * fast_route/fast_route/layers/stable_route.py:97-102. */
+int fr_combine(const void* y, int64_t ld_y, int dtype, const int32_t* inv_pos, int64_t M, int topk, int H,
+               int64_t max_rows, void* out, int64_t ld_out, void* stream);
+
+/* The whole layer on one stream: route -> align -> permute -> GEMM1+SiLU -> GEMM2 -> combine.
+ * Stands in for fused_moe, fast_route/fast_route/layers/stable_route.py:10-102.
+ * x[M,H], gate as in fr_route_fused, w1[E,2I,H], w2[E,H,I], out[M,H] (may alias x: the
+ * reference's inplace=True).  topk_weights_out / topk_ids_out (may be NULL) receive the
+ * compact routing.  The workspace holds every intermediate. */
+size_t fr_moe_workspace_bytes(int64_t M, int H, int I, int E, int topk);
+int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t gate_stride_e, const void* w1,
+                 const void* w2, int dtype, int64_t M, int H, int I, int E, int topk, int renormalize, void* out,
+                 float* topk_weights_out, int32_t* topk_ids_out, void* workspace, size_t workspace_bytes,
+                 void* stream);
+
+/* Expert-parallel building blocks (no counterpart in the reference, which is single-GPU).
+ * fr_moe_experts: the expert part of the layer for rows that already carry an expert id
+ * (tokens received from other ranks): align by local expert -> permute -> GEMM1+SiLU ->
+ * GEMM2 -> rows returned in the order they came in.  rows[R,H], row_expert[R] in
+ * [0, E_local), row_weight[R] (may be NULL), y[R,H]. */
+size_t fr_moe_experts_workspace_bytes(int64_t R, int H, int I, int E_local);
+int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row_weight, const void* w1,
+                   const void* w2, int dtype, int64_t R, int H, int I, int E_local, void* y, void* workspace,
+                   size_t workspace_bytes, void* stream);
+
+/* Gather rows by index: dst[i,:] = src[idx[i],:] (idx < 0 writes zeros); 16-byte vectors. */
+int fr_gather_rows(const void* src, int64_t ld_src, const int32_t* idx, int64_t rows, int row_bytes, void* dst,
+                   int64_t ld_dst, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FAST_ROUTE_SM100_H_ */

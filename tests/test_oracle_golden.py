@@ -1,0 +1,104 @@
+"""The CPU oracle against the golden vectors produced by the reference's own code
+(see tests/golden/make_golden.py for how they were made)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.mark.parametrize("E", [8, 16, 64, 128])
+@pytest.mark.parametrize("name", ["f16", "f32"])
+def test_stable_argsort_matches_reference_kernel(E, name):
+    g = np.load(os.path.join(GOLD, "stable_argsort.npz"))
+    x = g[f"x_{E}_{name}"]
+    vals, ids = oracle.stable_topk(x, E)
+    assert np.array_equal(ids, g[f"ids_{E}_{name}"])
+    assert np.array_equal(vals, g[f"sorted_{E}_{name}"])
+    # the vectors contain ties, otherwise the tie rule is not exercised
+    assert (np.diff(np.sort(x, axis=1), axis=1) == 0).any()
+
+
+@pytest.mark.parametrize("case", range(5))
+def test_route_matches_reference_kernel(case):
+    g = np.load(os.path.join(GOLD, "route_kernel.npz"))
+    M, K, E, k = (int(v) for v in g[f"meta_{case}"])
+    h = torch.from_numpy(g[f"h_{case}"])
+    gate = torch.from_numpy(g[f"g_{case}"])
+    w, ids, logits = oracle.route_from_hidden(h, gate, k)
+    assert np.array_equal(ids, g[f"ids_{case}"][:, :k])
+    # reference tolerance for the weights: atol 1e-2 (fast_route/tests/test_route.py:67-74);
+    # the restatement is far inside it
+    np.testing.assert_allclose(w, g[f"w_{case}"][:, :k], atol=2e-7, rtol=0)
+    wfull, idfull = oracle.full_argsort_fill(logits, k)
+    assert np.array_equal(idfull, g[f"ids_{case}"])
+    np.testing.assert_allclose(wfull, g[f"w_{case}"], atol=2e-7, rtol=0)
+
+
+def test_torch_moe_small_matches_reference_function():
+    g = np.load(os.path.join(GOLD, "torch_moe.npz"))
+    x, gate, w1, w2 = (torch.from_numpy(g[f"small_{n}"]) for n in ("x", "gate", "w1", "w2"))
+    out, w, ids = oracle.moe_layer(x, gate, w1, w2, 2)
+    assert np.array_equal(ids, g["small_ti"])
+    np.testing.assert_allclose(w, g["small_tw"], atol=2e-7, rtol=0)
+    np.testing.assert_allclose(out.numpy(), g["small_out"], atol=1e-6, rtol=1e-5)
+
+
+def test_torch_moe_reference_cpu_case():
+    """fp32, M=256, H=1024, I=2048, E=8, top-2, seed 0: the reference's CPU-runnable case."""
+    from fast_route_b200 import synth
+    g = np.load(os.path.join(GOLD, "torch_moe.npz"))
+    x, gate, w1, w2 = synth.moe_inputs(256, 1024, 2048, 8, seed=0, dtype=torch.float32)
+    sums = np.array([x.double().sum().item(), w1.double().sum().item(), w2.double().sum().item()])
+    np.testing.assert_allclose(sums, g["c1_x_sum"], rtol=1e-9, err_msg="seeded inputs differ from the ones the golden output was made from")
+    out, w, ids = oracle.moe_layer(x, gate, w1, w2, 2)
+    assert np.array_equal(ids, g["c1_ti"])
+    np.testing.assert_allclose(w, g["c1_tw"], atol=2e-7, rtol=0)
+    np.testing.assert_allclose(out[::8, ::16].numpy(), g["c1_out_sample"], atol=2e-5, rtol=1e-4)
+
+
+def test_align_docstring_example():
+    """Known answer from fast_route/fast_route/ops/fused_moe.py:151-159 (1-based experts there)."""
+    ids = np.array([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]]) - 1
+    s, e, n, c = oracle.moe_align_block_size(ids, 4, 4)
+    assert s[:16].tolist() == [3, 6, 9, 12, 0, 4, 10, 12, 1, 7, 11, 12, 2, 5, 8, 12]
+    assert e[:4].tolist() == [0, 1, 2, 3] and int(n[0]) == 16 and c.tolist() == [3, 3, 3, 3]
+
+
+def test_align_properties():
+    rng = np.random.default_rng(0)
+    for (n, E, bs) in [(0, 4, 16), (1, 8, 128), (1000, 64, 64), (777, 5, 7)]:
+        ids = rng.integers(0, E, size=n)
+        if E == 64:
+            ids[ids == 3] = 2          # an expert without tokens
+        s, e, npost, c = oracle.moe_align_block_size(ids, bs, E)
+        npost = int(npost[0])
+        assert npost % bs == 0 and npost == sum((int(x) + bs - 1) // bs * bs for x in c)
+        valid = s[:npost]
+        real = valid[valid < n]
+        assert sorted(real.tolist()) == list(range(n))
+        blocks = valid.reshape(-1, bs)
+        for b, row in enumerate(blocks):
+            r = row[row < n]
+            assert (ids[r] == e[b]).all() and (np.diff(r) > 0).all()
+        assert (s[npost:] == n).all()
+
+
+def test_exp_recipe_accuracy_and_tie_rule():
+    xs = np.linspace(-87, 0, 100001).astype(np.float32)
+    rel = np.abs(oracle.exp_recipe(xs) - np.exp(xs.astype(np.float64))) / np.exp(xs.astype(np.float64))
+    assert rel.max() < 2e-7
+    assert oracle.exp_recipe(np.float32(0.0)) == np.float32(1.0)
+    logits = np.array([[1.0, 2.0, 2.0, 0.5, 2.0, -0.0, 0.0, -1.0]], dtype=np.float32)
+    w, ids = oracle.topk_softmax(logits, 4)
+    assert ids.tolist() == [[1, 2, 4, 0]]
+    np.testing.assert_allclose(w.sum(), 1.0, atol=1e-6)
+    _, full = oracle.stable_topk(logits, 8)
+    assert full.tolist() == [[1, 2, 4, 0, 3, 5, 6, 7]]   # -0.0 and +0.0 tie -> lower id first
+    wt = torch.softmax(torch.sort(torch.from_numpy(logits), descending=True, stable=True)[0][:, :4], -1)
+    np.testing.assert_allclose(w, wt.numpy(), atol=1e-6)
