@@ -1,0 +1,477 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-routing MoE layer (Mixtral-8x7B shape by default).
+
+    python bench.py --gpus N --steps K --warmup W            # this library, N GPUs of one node
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's naive torch MoE on host cores
+
+One JSON line is printed by rank 0.  A step is one pass of the layer over one batch of
+synthetic tokens (x ~ N(0,1), weights ~ N(0, 0.02^2), bf16).  With N > 1 the experts are
+sharded over the ranks (expert parallel, NCCL all-to-all dispatch and combine) and every
+rank brings its own batch of M tokens (weak scaling in tokens).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+WORKLOADS = {
+    # name: (H, I, E, topk)
+    "mixtral-8x7b": (4096, 14336, 8, 2),
+    "mixtral-8x22b": (6144, 16384, 8, 2),
+    "fine-grained-64e": (2048, 1408, 64, 6),
+}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        p["source"] = "measured"
+        return p
+    p = dict(FALLBACK_PEAKS)
+    p["source"] = "fallback"
+    return p
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index=0):
+        self.proc = None
+        self.path = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            self.sel = ["-i", uuid]
+        except Exception:
+            self.sel = []
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "50"] + self.sel, stdout=open(self.path, "w"),
+                                         stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        try:
+            for line in open(self.path):
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) < 8:
+                    continue
+                try:
+                    sm.append(float(parts[0]))
+                    mx.append(float(parts[1]))
+                    power.append(float(parts[2]))
+                except ValueError:
+                    continue
+                for nm, val in zip(names, parts[4:8]):
+                    if val.lower().startswith("active"):
+                        reasons.add(nm)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(power))
+        return out
+
+
+def cuda_time_ms(fn, reps, warm=3):
+    """Median and min device time of fn() over reps launches (CUDA events on the current stream)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    return statistics.median(ts), ts[0]
+
+
+def make_weights(H, I, E, device, seed=0, dtype=torch.bfloat16, experts=None):
+    """Random-init weights of the layer (N(0, 0.02^2)), generated on `device`."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    ne = E if experts is None else len(experts)
+    w1 = torch.empty(ne, 2 * I, H, dtype=dtype, device=device)
+    w2 = torch.empty(ne, H, I, dtype=dtype, device=device)
+    for e in range(ne):
+        w1[e].copy_(torch.randn(2 * I, H, generator=g, device=device, dtype=torch.float32) * 0.02)
+        w2[e].copy_(torch.randn(H, I, generator=g, device=device, dtype=torch.float32) * 0.02)
+    wg = (torch.randn(E, H, generator=g, device=device, dtype=torch.float32) * 0.02).to(dtype)
+    return wg, w1, w2
+
+
+# --------------------------------------------------------------------------------------
+# CPU baseline: the reference's naive torch MoE (restated in oracle/), host cores
+# --------------------------------------------------------------------------------------
+def cpu_reference_rate(H, I, E, k, sample_tokens, reps, warm=1, weights=None, budget_s=None):
+    """Tokens/s of the reference's naive layer on the host cores.  One pass = router (fp32 logits,
+    stable top-k, softmax over the k) + per-expert masked matmuls, fp32, on `sample_tokens` tokens.
+    With `budget_s` the sample is shrunk so that warm + reps passes fit the budget."""
+    import oracle
+    threads = os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    if weights is None:
+        gen_dev = "cuda" if torch.cuda.is_available() else "cpu"
+        wg, w1, w2 = make_weights(H, I, E, gen_dev, seed=0)
+    else:
+        wg, w1, w2 = weights
+    wg, w1, w2 = wg.cpu().float(), w1.cpu().float(), w2.cpu().float()
+    gate = wg.t()
+    gen = torch.Generator().manual_seed(1)
+    probe = torch.randn(64, H, generator=gen)
+    oracle.moe_layer(probe, gate, w1, w2, k)          # warms the thread pool
+    t0 = time.perf_counter()
+    oracle.moe_layer(probe, gate, w1, w2, k)
+    per_token = (time.perf_counter() - t0) / 64
+    if budget_s is not None:
+        fit = int(budget_s / max(per_token, 1e-9) / max(1, warm + reps))
+        sample_tokens = max(64, min(sample_tokens, fit // 64 * 64))
+    x = torch.randn(sample_tokens, H, generator=gen)
+    for _ in range(warm):
+        oracle.moe_layer(x, gate, w1, w2, k)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        oracle.moe_layer(x, gate, w1, w2, k)
+        times.append(time.perf_counter() - t0)
+    t = statistics.median(times)
+    return {"value": sample_tokens / t, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{sample_tokens} tokens of the same layer shape per pass, fp32, median of {reps} passes "
+                      f"({t * 1e3:.0f} ms each); router + per-expert masked matmuls as in the reference's torch_moe",
+            "ms_per_sample": t * 1e3, "total_s": sum(times)}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's own CPU path (its naive torch MoE, restated in oracle/
+    because the reference tree is not present where the benchmark runs) on all host threads."""
+    if rank != 0:
+        return
+    H, I, E, k = WORKLOADS[args.workload]
+    r = cpu_reference_rate(H, I, E, k, args.cpu_tokens, max(1, args.steps), warm=min(args.warmup, 2),
+                           budget_s=args.cpu_budget)
+    line = {
+        "impl": "reference", "metric": "moe_layer_tokens_per_s", "value": r["value"], "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": r["ms_per_sample"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{args.workload} MoE layer H={H} I={I} E={E} top-{k}, M={args.tokens} tokens per GPU "
+                               f"per step; each CPU step is a bounded sample of that batch (see cpu_baseline.sample)"},
+        "cpu_baseline": {k_: r[k_] for k_ in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": r["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# --------------------------------------------------------------------------------------
+# this library
+# --------------------------------------------------------------------------------------
+def sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms):
+    """Layer time vs M.  `ms` is the eager call (Python + 6-8 launches per call); `ms_graph` replays
+    the same call captured in a CUDA graph (no host work between kernels) - the number the
+    roofline fractions use, since at small M the eager time is host launch overhead."""
+    rows = []
+    dev = w1.device
+    for M in Ms:
+        x = torch.randn(M, H, device=dev, dtype=w1.dtype)
+        _, _, ti = fr.fused_moe(x, wg.t(), w1, w2, k, return_routing=True)
+        active = int(torch.unique(ti).numel())
+        reps = 20 if M <= 1024 else 8
+        med, _ = cuda_time_ms(lambda: fr.fused_moe(x, wg.t(), w1, w2, k), reps)
+        out = torch.empty_like(x)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            out = fr.fused_moe(x, wg.t(), w1, w2, k)
+        gmed, _ = cuda_time_ms(g.replay, reps)
+        flops = synth.layer_flops(M, H, I, E, k)
+        nbytes = synth.layer_bytes(active, M, H, I, E)
+        rows.append({"M": M, "ms": round(med, 4), "ms_graph": round(gmed, 4), "tokens_per_s": M / gmed * 1e3,
+                     "tflops": flops / gmed / 1e9, "frac_tensor_peak": flops / gmed / 1e9 / peaks["bf16_tflops"],
+                     "active_experts": active, "hbm_gbs": nbytes / gmed / 1e6,
+                     "frac_hbm_peak": nbytes / gmed / 1e6 / peaks["hbm_gbs"],
+                     "ref_convention_tflops": 2.0 * M * I * H / gmed / 1e9})
+        del g
+    return rows
+
+
+def routing_latency(fr, synth, dev):
+    from fast_route_b200 import _lib
+    lib = _lib.load()
+    out = []
+    for E, k in ((8, 2), (64, 6), (128, 8)):
+        M, bs = 16384, 64
+        lg = synth.routing_logits(M, E, k, seed=1, dtype=torch.float16).to(dev)
+        n = M * k
+        w = torch.empty(M, k, dtype=torch.float32, device=dev)
+        ids = torch.empty(M, k, dtype=torch.int32, device=dev)
+        s = torch.empty(n + E * (bs - 1), dtype=torch.int32, device=dev)
+        e = torch.empty(n + E, dtype=torch.int32, device=dev)
+        npost = torch.empty(1, dtype=torch.int32, device=dev)
+
+        def call():
+            rc = lib.fr_route_align(_lib.ptr(lg), 0, M, E, lg.stride(0), 1, k, _lib.ptr(w), _lib.ptr(ids), bs,
+                                    _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(), _lib.ptr(npost),
+                                    _lib.stream_ptr(dev))
+            assert rc == 0, rc
+        med, _ = cuda_time_ms(call, 50, 5)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            call()
+        gmed, _ = cuda_time_ms(g.replay, 50, 5)
+
+        def call_topk():
+            rc = lib.fr_topk_softmax(_lib.ptr(lg), 0, M, E, lg.stride(0), 1, k, 1, _lib.ptr(w), k, _lib.ptr(ids), k, 0,
+                                     _lib.stream_ptr(dev))
+            assert rc == 0, rc
+
+        def call_align():
+            rc = lib.fr_align(_lib.ptr(ids), n, E, bs, _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(), _lib.ptr(npost),
+                              None, None, _lib.stream_ptr(dev))
+            assert rc == 0, rc
+        parts = []
+        for fn in (call_topk, call_align):
+            gg = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gg):
+                for _ in range(10):
+                    fn()
+            parts.append(cuda_time_ms(gg.replay, 20, 3)[0] * 100.0)   # us per launch (10 launches per replay)
+        nbytes = M * E * 2 + M * k * 8 + M * k * 4 + 4 * (int(npost.item()) + int(npost.item()) // bs + 1)
+        out.append({"tokens": M, "E": E, "topk": k, "block": bs, "us": med * 1e3, "us_graph": gmed * 1e3,
+                    "us_topk_kernel": parts[0], "us_align_kernel": parts[1], "algorithmic_bytes": nbytes})
+    return out
+
+
+def gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps):
+    """Times the dominant kernel (grouped GEMM 1 + SiLU*mul epilogue) alone through the C ABI."""
+    from fast_route_b200.ops import fused_moe as fm
+    dev = w1.device
+    x = torch.randn(M, H, device=dev, dtype=w1.dtype)
+    tw, ti = fr.fused_route(x, wg.t(), k)
+    s, e, npost, cnt, inv = fm.moe_align_block_size(ti, 128, E, return_extra=True)
+    n = M * k
+    rows = (n + min(n, E) * 127 + 127) // 128 * 128
+    a = fm.permute_rows(x, s, npost, k, max_rows=rows)
+    med, mn = cuda_time_ms(lambda: fm.gemm1_silu(a, w1, e, npost, s, n), reps)
+    flops = 4.0 * n * H * I
+    return {"bound": "tensor", "kernel": "grouped_gemm_kernel<256,4,SILU,bf16> (GEMM1 + SiLU*mul)",
+            "achieved": flops / med / 1e9, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+            "frac": flops / med / 1e9 / peaks["bf16_tflops"],
+            "frac_of_sustained_peak": flops / med / 1e9 / peaks["bf16_tflops_sustained"],
+            "peak_source": peaks["source"] + " (burst cuBLAS bf16; kernel timed alone)",
+            "ms_per_launch": med, "algorithmic_flops_per_launch": flops, "traffic": None}
+
+
+def run_ours(args, rank, world, local_rank):
+    import fast_route_b200 as fr
+    from fast_route_b200 import synth, _lib
+    import torch.distributed as dist
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    H, I, E, k = WORKLOADS[args.workload]
+    M = args.tokens
+    peaks = load_peaks()
+    dtype = torch.bfloat16
+
+    if args.routing_only:
+        print(json.dumps({"routing_latency": routing_latency(fr, synth, dev)}), flush=True)
+        return
+
+    if world > 1:
+        from fast_route_b200.parallel import ep
+        assert E % world == 0, "experts must divide over the ranks"
+        group = ep.ExpertParallelGroup(dist.group.WORLD, E)
+        lo, hi = group.local_expert_range()
+        wg, w1, w2 = make_weights(H, I, E, dev, seed=0, experts=list(range(lo, hi)))
+        # the gate is replicated: same seed stream on every rank would differ after the experts, so broadcast it
+        dist.broadcast(wg, src=0)
+
+        def layer(xb):
+            return ep.fused_moe_ep(xb, wg.t(), w1, w2, k, group)
+        launches_per_step = 12
+    else:
+        wg, w1, w2 = make_weights(H, I, E, dev, seed=0)
+
+        def layer(xb):
+            return fr.fused_moe(xb, wg.t(), w1, w2, k)
+        launches_per_step = 6
+
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    xs = [torch.randn(M, H, device=dev, dtype=dtype, generator=g) for _ in range(3)]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput -------------------------------------------------
+    for i in range(args.warmup):
+        layer(xs[i % 3])
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        layer(xs[i % 3])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    total_tokens = M * world
+    value = total_tokens / ms_per_step * 1e3
+    _lib.raise_on_device_error()
+
+    if args.profile:
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "ms_per_step": ms_per_step, "tokens_per_s": value}), flush=True)
+        return
+
+    # ---- end to end through the public API with host buffers ------------------------
+    hx = [torch.randn(M, H, dtype=dtype).pin_memory() for _ in range(2)]
+    hout = torch.empty(M, H, dtype=dtype).pin_memory()
+    dx = torch.empty(M, H, dtype=dtype, device=dev)
+
+    def e2e_step(i):
+        dx.copy_(hx[i % 2], non_blocking=True)
+        out = layer(dx)
+        hout.copy_(out, non_blocking=True)
+    for i in range(max(1, min(args.warmup, 3))):
+        e2e_step(i)
+    barrier()
+    e0.record()
+    for i in range(args.steps):
+        e2e_step(i)
+    e1.record()
+    barrier()
+    ems = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ems], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ems = float(t.item())
+    e2e = {"value": total_tokens / (ems / args.steps) * 1e3, "unit": "tokens/s",
+           "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2 * world,
+           "ms_per_step": ems / args.steps}
+
+    if rank != 0:
+        return
+    flops = synth.layer_flops(total_tokens, H, I, E, k)
+    line = {
+        "metric": "moe_layer_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload} MoE layer H={H} I={I} E={E} top-{k}, M={M} tokens per GPU per step",
+                   "parallelism": "single GPU" if world == 1 else f"expert parallel ep{world} + token data parallel",
+                   "l2": "weights (2.8 GB) and activations far exceed the 126 MB L2; no explicit flush",
+                   "tokens_per_step_total": total_tokens},
+        "tflops": flops / ms_per_step / 1e9,
+        "frac_tensor_peak": flops / ms_per_step / 1e9 / (peaks["bf16_tflops_sustained"] * world),
+        "frac_tensor_peak_note": f"of {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_tflops_sustained']} TF/GPU)",
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+    }
+    if world == 1:
+        line["roofline"] = gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps=max(5, args.steps))
+        traffic_file = os.path.join(ROOT, "profiles", "gemm1_traffic.json")
+        if os.path.exists(traffic_file):
+            with open(traffic_file) as f:
+                tr = json.load(f)
+            # measured DRAM bytes of a smaller launch, scaled by rows x weight bytes
+            line["roofline"]["traffic"] = tr.get("traffic_bytes_per_launch_scaled")
+            line["roofline"]["traffic_note"] = tr.get("note")
+        if not args.no_sweep:
+            Ms = [m for m in (1, 4, 16, 64, 256, 1024, 4096, 16384)]
+            line["sweep"] = sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms)
+            line["routing_latency"] = routing_latency(fr, synth, dev)
+        if not args.no_cpu:
+            cb = cpu_reference_rate(H, I, E, k, args.cpu_tokens, 3, warm=1, weights=(wg, w1, w2), budget_s=20.0)
+            line["cpu_baseline"] = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+    _lib.raise_on_device_error()
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="mixtral-8x7b", choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", "-m", type=int, default=16384, help="tokens per GPU per step")
+    ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens in the CPU baseline's sample")
+    ap.add_argument("--cpu-budget", type=float, default=120.0,
+                    help="seconds the reference arm may spend in its timed passes (the sample shrinks to fit)")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--routing-only", action="store_true",
+                    help="only the routing/align latency microbenchmark (16384 tokens, E in 8/64/128)")
+    ap.add_argument("--profile", action="store_true",
+                    help="only warm-up + timed layer steps (for ncu captures): no e2e, sweep, roofline or CPU legs")
+    args = ap.parse_args()
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -15,7 +15,9 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st);
+                          cudaStream_t st, int* deferred_split);
+int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, const float* topk_w,
+                             int64_t M, int topk, int dtype, void* out, int64_t ld_out, cudaStream_t st);
 int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate_km,
                          int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
                          int32_t* ids, float* logits_out, cudaStream_t st);
@@ -97,6 +99,92 @@ __global__ void transpose_gate_kernel(const uint16_t* __restrict__ gate, int64_t
   out[i] = h < H ? gate[h * sh + e * se] : static_cast<uint16_t>(0);
 }
 
+// Router for a handful of rows (decode-sized batches): one CTA per token, the H-long dot
+// products are split over the threads (fp32 FMA, fixed reduction order), then warp 0 ranks
+// the E logits by counting (ties -> lower expert id) and writes the top-k and its softmax.
+// A 128-row tensor-core tile would leave 147 SMs idle and walk H serially on one.
+template <bool BF16>
+__global__ void __launch_bounds__(256) router_small_kernel(const uint16_t* __restrict__ x, int64_t ldx,
+                                                           const uint16_t* __restrict__ gate_km, int64_t ld_gate,
+                                                           int H, int E, int topk, int renormalize,
+                                                           float* __restrict__ weights, int32_t* __restrict__ ids,
+                                                           float* __restrict__ logits_out) {
+  extern __shared__ float rs[];
+  float* part = rs;                 // [8 warps][E]
+  float* logit = rs + 8 * E;        // [E]
+  float* byrank = logit + E;        // [E]
+  const int64_t row = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint16_t* xr = x + row * ldx;
+  for (int e0 = 0; e0 < E; e0 += 8) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (int h = threadIdx.x * 8; h < H; h += 256 * 8) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(xr + h);
+      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        if (e0 + i < E) {
+          const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gate_km + static_cast<int64_t>(e0 + i) * ld_gate + h));
+          const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 a = unpack2<BF16>(xw[q]);
+            const float2 b = unpack2<BF16>(gw[q]);
+            acc[i] = fmaf(a.x, b.x, acc[i]);
+            acc[i] = fmaf(a.y, b.y, acc[i]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float v = acc[i];
+      for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+      if (lane == 0 && e0 + i < E) part[warp * E + e0 + i] = v;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += 256) {
+    float v = 0.0f;
+    for (int w = 0; w < 8; ++w) v += part[w * E + e];
+    if (v != v) v = -INFINITY;
+    logit[e] = v;
+    if (logits_out) logits_out[row * E + e] = v;
+  }
+  __syncthreads();
+  if (warp != 0 || !weights) return;
+  for (int c = lane; c < E; c += 32) {
+    const float v = logit[c];
+    int rank = 0;
+    for (int o = 0; o < E; ++o) {
+      const float ov = logit[o];
+      rank += (ov > v || (ov == v && o < c)) ? 1 : 0;
+    }
+    byrank[rank] = v;
+    if (rank < topk) ids[row * topk + rank] = c;
+  }
+  __syncwarp();
+  const float top = byrank[0];
+  float s;
+  if (renormalize) {
+    s = 0.0f;
+    for (int j = 0; j < topk; ++j) {
+      const float ej = exp_recipe(__fsub_rn(byrank[j], top));
+      s = (j == 0) ? ej : __fadd_rn(s, ej);
+    }
+  } else {
+    float psum = 0.0f;
+    for (int c = lane; c < E; c += 32) psum += exp_recipe(__fsub_rn(logit[c], top));
+    for (int off = 16; off > 0; off >>= 1) psum += __shfl_xor_sync(0xffffffffu, psum, off);
+    s = psum;
+  }
+  for (int j = lane; j < topk; j += 32) weights[row * topk + j] = __fdiv_rn(exp_recipe(__fsub_rn(byrank[j], top)), s);
+}
+
+constexpr int kSmallRouterRows = 32;
+
 // ----------------------------------------------------------------------------------
 // workspace carving
 // ----------------------------------------------------------------------------------
@@ -176,6 +264,19 @@ static int route_fused_impl(const void* x, int dtype, int64_t M, int H, int64_t 
     gate_km = ws.gate_km;
     ld_gate = ws.ld_gate;
   }
+  if (M <= kSmallRouterRows && (H % 8) == 0 && (ldx % 8) == 0 && (ld_gate % 8) == 0 && E <= 1024 &&
+      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(gate_km) & 15) == 0) {
+    const size_t smem = static_cast<size_t>(10) * E * sizeof(float);
+    if (dtype == FR_BF16)
+      router_small_kernel<true><<<static_cast<unsigned>(M), 256, smem, st>>>(
+          static_cast<const uint16_t*>(x), ldx, static_cast<const uint16_t*>(gate_km), ld_gate, H, E, topk,
+          renormalize, weights, ids, logits_out);
+    else
+      router_small_kernel<false><<<static_cast<unsigned>(M), 256, smem, st>>>(
+          static_cast<const uint16_t*>(x), ldx, static_cast<const uint16_t*>(gate_km), ld_gate, H, E, topk,
+          renormalize, weights, ids, logits_out);
+    return static_cast<int>(cudaGetLastError());
+  }
   if (topk <= 8) {
     return router_gemm_dispatch(x, dtype, M, H, ldx, gate_km, ld_gate, E, topk, renormalize, 1, weights, ids,
                                 logits_out, st);
@@ -226,11 +327,14 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
       H / 8, row_v);
   FR_CUDA_OK(cudaGetLastError());
   rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
-                             w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st);
+                             w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
   if (rc) return rc;
+  int deferred = 0;
   rc = gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
-                             weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st);
+                             weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred);
   if (rc) return rc;
+  if (deferred > 1)  // split-K GEMM2: its reduction, the routed weights and the sum over slots in one kernel
+    return combine_partial_dispatch(w.split, deferred, n, H, weights, M, topk, dtype, out, ld_out, st);
   if (dtype == FR_BF16)
     combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
         reinterpret_cast<const uint4*>(w.y_sorted), H / 8, w.inv_pos, topk, row_v, w.rows,
@@ -351,7 +455,7 @@ int fr_gemm1_silu(const void* a_sorted, int64_t lda, const void* w1, int dtype, 
                   void* stream) {
   return gemm_grouped_dispatch(0, a_sorted, lda, w1, dtype, max_rows, H, I, E, 2 * I, expert_ids,
                                num_tokens_post_pad, sorted_ids, nullptr, n, act, ld_act, split_k, workspace,
-                               workspace_bytes, static_cast<cudaStream_t>(stream));
+                               workspace_bytes, static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int fr_gemm2(const void* act, int64_t ld_act, const void* w2, int dtype, int64_t max_rows, int H, int I, int E,
@@ -360,7 +464,7 @@ int fr_gemm2(const void* act, int64_t ld_act, const void* w2, int dtype, int64_t
              size_t workspace_bytes, void* stream) {
   return gemm_grouped_dispatch(1, act, ld_act, w2, dtype, max_rows, I, H, E, H, expert_ids, num_tokens_post_pad,
                                sorted_ids, topk_weights, n, y, ld_y, split_k, workspace, workspace_bytes,
-                               static_cast<cudaStream_t>(stream));
+                               static_cast<cudaStream_t>(stream), nullptr);
 }
 
 int fr_combine(const void* y, int64_t ld_y, int dtype, const int32_t* inv_pos, int64_t M, int topk, int H,

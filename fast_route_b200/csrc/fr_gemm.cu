@@ -296,54 +296,78 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 // ----------------------------------------------------------------------------------
 // split-K reductions (small M): sum the fp32 partials in split order, apply the epilogue.
 // ----------------------------------------------------------------------------------
+// grid = (column chunks of 1024, sorted rows); padding rows are left untouched (nothing reads them)
 template <bool BF16>
-__global__ void splitk_reduce_silu_kernel(const float* __restrict__ partial, int64_t partial_cols, int split_k,
-                                          int64_t n_valid, const int32_t* __restrict__ sorted_ids,
-                                          const int32_t* __restrict__ num_post, int I, int half_tile,
-                                          uint16_t* __restrict__ act, int64_t ld_act) {
-  const int64_t row = blockIdx.x;
+__global__ void __launch_bounds__(256)
+splitk_reduce_silu_kernel(const float* __restrict__ partial, int64_t partial_cols, int split_k, int64_t n_valid,
+                          const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post, int I,
+                          int half_tile, uint16_t* __restrict__ act, int64_t ld_act) {
+  const int64_t row = blockIdx.y;
   if (row >= __ldg(num_post)) return;
   const int32_t sid = __ldg(sorted_ids + row);
-  const bool valid = sid >= 0 && sid < n_valid;
-  for (int j = threadIdx.x * 2; j < I; j += blockDim.x * 2) {
-    float g0 = 0.f, g1 = 0.f, u0 = 0.f, u1 = 0.f;
-    if (valid) {
-      const int nb = j / half_tile, c = j % half_tile;
-      const int64_t gcol = static_cast<int64_t>(nb) * 2 * half_tile + c;
-      for (int s = 0; s < split_k; ++s) {
-        const float* pr = partial + (static_cast<int64_t>(s) * n_valid + sid) * partial_cols;
-        const float2 g = *reinterpret_cast<const float2*>(pr + gcol);
-        const float2 u = *reinterpret_cast<const float2*>(pr + gcol + half_tile);
-        g0 += g.x; g1 += g.y; u0 += u.x; u1 += u.y;
-      }
-    }
-    *reinterpret_cast<uint32_t*>(act + row * ld_act + j) = pack2<BF16>(silu_f(g0) * u0, silu_f(g1) * u1);
+  if (sid < 0 || sid >= n_valid) return;
+  const int j = (blockIdx.x * 256 + threadIdx.x) * 4;  // half_tile is a multiple of 4: no straddling
+  if (j >= I) return;
+  const int nb = j / half_tile, c = j % half_tile;
+  const int64_t gcol = static_cast<int64_t>(nb) * 2 * half_tile + c;
+  float4 g = make_float4(0.f, 0.f, 0.f, 0.f), u = g;
+  for (int s = 0; s < split_k; ++s) {
+    const float* pr = partial + (static_cast<int64_t>(s) * n_valid + sid) * partial_cols + gcol;
+    const float4 gs = *reinterpret_cast<const float4*>(pr);
+    const float4 us = *reinterpret_cast<const float4*>(pr + half_tile);
+    g.x += gs.x; g.y += gs.y; g.z += gs.z; g.w += gs.w;
+    u.x += us.x; u.y += us.y; u.z += us.z; u.w += us.w;
   }
+  *reinterpret_cast<uint2*>(act + row * ld_act + j) =
+      make_uint2(pack2<BF16>(silu_f(g.x) * u.x, silu_f(g.y) * u.y), pack2<BF16>(silu_f(g.z) * u.z, silu_f(g.w) * u.w));
 }
 
 template <bool BF16>
-__global__ void splitk_reduce_weighted_kernel(const float* __restrict__ partial, int64_t partial_cols,
-                                              int split_k, int64_t n_valid,
-                                              const int32_t* __restrict__ sorted_ids,
-                                              const int32_t* __restrict__ num_post,
-                                              const float* __restrict__ topk_w, int H,
-                                              uint16_t* __restrict__ y, int64_t ld_y) {
-  const int64_t row = blockIdx.x;
+__global__ void __launch_bounds__(256)
+splitk_reduce_weighted_kernel(const float* __restrict__ partial, int64_t partial_cols, int split_k, int64_t n_valid,
+                              const int32_t* __restrict__ sorted_ids, const int32_t* __restrict__ num_post,
+                              const float* __restrict__ topk_w, int H, uint16_t* __restrict__ y, int64_t ld_y) {
+  const int64_t row = blockIdx.y;
   if (row >= __ldg(num_post)) return;
   const int32_t sid = __ldg(sorted_ids + row);
-  const bool valid = sid >= 0 && sid < n_valid;
-  const float w = valid ? (topk_w ? __ldg(topk_w + sid) : 1.0f) : 0.0f;
-  for (int j = threadIdx.x * 2; j < H; j += blockDim.x * 2) {
-    float a0 = 0.f, a1 = 0.f;
-    if (valid) {
-      for (int s = 0; s < split_k; ++s) {
-        const float2 a = *reinterpret_cast<const float2*>(
-            partial + (static_cast<int64_t>(s) * n_valid + sid) * partial_cols + j);
-        a0 += a.x; a1 += a.y;
-      }
-    }
-    *reinterpret_cast<uint32_t*>(y + row * ld_y + j) = pack2<BF16>(w * a0, w * a1);
+  if (sid < 0 || sid >= n_valid) return;
+  const int j = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (j >= H) return;
+  const float w = topk_w ? __ldg(topk_w + sid) : 1.0f;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int s = 0; s < split_k; ++s) {
+    const float4 v = *reinterpret_cast<const float4*>(
+        partial + (static_cast<int64_t>(s) * n_valid + sid) * partial_cols + j);
+    a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
   }
+  *reinterpret_cast<uint2*>(y + row * ld_y + j) =
+      make_uint2(pack2<BF16>(w * a.x, w * a.y), pack2<BF16>(w * a.z, w * a.w));
+}
+
+// Split-K GEMM2 with the reduction folded into the combine:
+// out[t,h] = sum_j w[t*k+j] * sum_s partial[s][t*k+j][h]   (slot order, slice order, fp32)
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+combine_partial_kernel(const float* __restrict__ partial, int64_t partial_cols, int split_k, int64_t n_valid,
+                       const float* __restrict__ topk_w, int topk, int H, uint16_t* __restrict__ out,
+                       int64_t ld_out) {
+  const int64_t t = blockIdx.y;
+  const int j = (blockIdx.x * 256 + threadIdx.x) * 4;
+  if (j >= H) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int q = 0; q < topk; ++q) {
+    const int64_t sid = t * topk + q;
+    const float w = topk_w ? __ldg(topk_w + sid) : 1.0f;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < split_k; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(
+          partial + (static_cast<int64_t>(s) * n_valid + sid) * partial_cols + j);
+      a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+    }
+    acc.x += w * a.x; acc.y += w * a.y; acc.z += w * a.z; acc.w += w * a.w;
+  }
+  *reinterpret_cast<uint2*>(out + t * ld_out + j) =
+      make_uint2(pack2<BF16>(acc.x, acc.y), pack2<BF16>(acc.z, acc.w));
 }
 
 // ----------------------------------------------------------------------------------
@@ -427,8 +451,11 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st) {
-  // which: 0 = GEMM1 (two-box B, SiLU epilogue), 1 = GEMM2 (weighted epilogue)
+                          cudaStream_t st, int* deferred_split) {
+  // which: 0 = GEMM1 (two-box B, SiLU epilogue), 1 = GEMM2 (weighted epilogue).
+  // deferred_split (GEMM2 only, may be null): when split-K is used, skip the reduction and
+  // report the slice count; the caller then finishes with combine_partial_dispatch.
+  if (deferred_split) *deferred_split = 0;
   if (!a || !w || !expert_ids || !num_post || !out || max_rows <= 0 || K <= 0 || n_out <= 0 || E <= 0)
     return FR_ERR_ARG;
   if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
@@ -484,25 +511,29 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
     rc = bf ? launch_grouped<MODE_PARTIAL, true>(tmA, tmB, p, grid, st)
             : launch_grouped<MODE_PARTIAL, false>(tmA, tmB, p, grid, st);
     if (rc) return rc;
-    const unsigned rows = static_cast<unsigned>(max_rows);
+    if (which == 1 && deferred_split) {
+      *deferred_split = split_k;
+      return FR_OK;
+    }
+    const dim3 rgrid(static_cast<unsigned>((n_out + 1023) / 1024), static_cast<unsigned>(max_rows));
     if (which == 0) {
       if (bf)
-        splitk_reduce_silu_kernel<true><<<rows, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
-                                                              sorted_ids, num_post, n_out, GEMM_BN / 2,
-                                                              static_cast<uint16_t*>(out), ldo);
-      else
-        splitk_reduce_silu_kernel<false><<<rows, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
+        splitk_reduce_silu_kernel<true><<<rgrid, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
                                                                sorted_ids, num_post, n_out, GEMM_BN / 2,
                                                                static_cast<uint16_t*>(out), ldo);
+      else
+        splitk_reduce_silu_kernel<false><<<rgrid, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
+                                                                sorted_ids, num_post, n_out, GEMM_BN / 2,
+                                                                static_cast<uint16_t*>(out), ldo);
     } else {
       if (bf)
-        splitk_reduce_weighted_kernel<true><<<rows, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
-                                                                  sorted_ids, num_post, topk_w, n_out,
-                                                                  static_cast<uint16_t*>(out), ldo);
-      else
-        splitk_reduce_weighted_kernel<false><<<rows, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
+        splitk_reduce_weighted_kernel<true><<<rgrid, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
                                                                    sorted_ids, num_post, topk_w, n_out,
                                                                    static_cast<uint16_t*>(out), ldo);
+      else
+        splitk_reduce_weighted_kernel<false><<<rgrid, 256, 0, st>>>(p.partial, p.partial_cols, split_k, n_valid,
+                                                                    sorted_ids, num_post, topk_w, n_out,
+                                                                    static_cast<uint16_t*>(out), ldo);
     }
     return static_cast<int>(cudaGetLastError());
   }
@@ -513,12 +544,26 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
             : launch_grouped<MODE_WEIGHTED, false>(tmA, tmB, p, grid, st);
 }
 
+int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, const float* topk_w,
+                             int64_t M, int topk, int dtype, void* out, int64_t ld_out, cudaStream_t st) {
+  const int64_t partial_cols = static_cast<int64_t>((n_out + GEMM_BN - 1) / GEMM_BN) * GEMM_BN;
+  const dim3 grid(static_cast<unsigned>((n_out + 1023) / 1024), static_cast<unsigned>(M));
+  if (dtype == FR_BF16)
+    combine_partial_kernel<true><<<grid, 256, 0, st>>>(static_cast<const float*>(workspace), partial_cols, split_k,
+                                                       n_valid, topk_w, topk, n_out, static_cast<uint16_t*>(out),
+                                                       ld_out);
+  else
+    combine_partial_kernel<false><<<grid, 256, 0, st>>>(static_cast<const float*>(workspace), partial_cols, split_k,
+                                                        n_valid, topk_w, topk, n_out, static_cast<uint16_t*>(out),
+                                                        ld_out);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // ==================================================================================
 // Fused router: one 128-row tile per CTA, N = padded expert count, whole K loop, then
 // each epilogue thread owns one row of logits in TMEM and selects its top-k in registers.
 // ==================================================================================
 constexpr int RKMAX = 8;
-constexpr int ROUTER_STAGES = 6;
 
 struct RouterParams {
   int64_t M;
@@ -534,8 +579,9 @@ struct RouterParams {
 
 template <int NPAD>
 struct RouterSmem {
+  static constexpr int STAGES = NPAD > 128 ? 4 : 6;  // 4 x 48 KB or 6 x <= 32 KB
   static constexpr int B_STAGE_BYTES = NPAD * BK * 2;
-  static constexpr int TOTAL = ROUTER_STAGES * (A_STAGE_BYTES + (B_STAGE_BYTES < 1024 ? 1024 : B_STAGE_BYTES)) + 256 + 1024;
+  static constexpr int TOTAL = STAGES * (A_STAGE_BYTES + (B_STAGE_BYTES < 1024 ? 1024 : B_STAGE_BYTES)) + 256 + 1024;
 };
 
 template <int NPAD, bool BF16>
@@ -543,6 +589,7 @@ __global__ void __launch_bounds__(192, 1)
 router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG,
                    const RouterParams p) {
   using SM = RouterSmem<NPAD>;
+  constexpr int ROUTER_STAGES = SM::STAGES;
   constexpr int B_STRIDE = SM::B_STAGE_BYTES < 1024 ? 1024 : SM::B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));

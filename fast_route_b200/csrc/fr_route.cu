@@ -238,11 +238,24 @@ int topk_softmax_dispatch(const void* logits, int dtype, int64_t M, int E, int64
 // align: one thread-block cluster (1..8 CTAs) sorts all n ids.  Warp g of the cluster owns
 // the contiguous slice [g*seg, (g+1)*seg) of the flat ids, so (cta, warp, row-of-32, lane)
 // order is flat-index order and the sort is stable by construction.
-//   pass 1: per-warp per-expert counts (match_any groups, one writer per group)
+//   pass 1: per-warp per-expert counts (groups of lanes with equal ids, one writer per group)
 //   exchange: CTA totals through distributed shared memory; every CTA derives the padded
 //             expert starts and its own base offsets
 //   pass 2: each id gets base[warp][e] + rank inside its match group
 // ----------------------------------------------------------------------------------
+// Lanes of the warp holding the same expert id (0 for lanes without a valid id).  One ballot
+// per id bit: constant cost, whereas the hardware match instruction slows down with the
+// number of distinct values in the warp (up to 32 with many experts).
+__device__ __forceinline__ unsigned same_expert_lanes(int e, int nbits) {
+  unsigned peers = __ballot_sync(0xffffffffu, e >= 0);
+  for (int b = 0; b < nbits; ++b) {
+    const bool bit = (e >> b) & 1;
+    const unsigned bal = __ballot_sync(0xffffffffu, bit);
+    peers &= bit ? bal : ~bal;
+  }
+  return e >= 0 ? peers : 0u;
+}
+
 struct AlignParams {
   const int32_t* ids;
   int64_t n;
@@ -256,8 +269,12 @@ struct AlignParams {
   int32_t* counts;
   int32_t* inv_pos;
   int64_t seg;  // ids per warp, multiple of 32
+  int nbits;    // bits needed for an expert id
 };
 
+// ITERS > 0: a warp's slice is at most ITERS rows of 32 ids and is loaded once into
+// registers (all loads in flight together); ITERS == 0: any length, ids re-read per pass.
+template <int ITERS>
 __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
   extern __shared__ int sm_i[];
   cg::cluster_group cluster = cg::this_cluster();
@@ -281,19 +298,46 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
   const int64_t hi = (lo + p.seg < p.n) ? lo + p.seg : p.n;
   int* my = cnt + warp * E;
 
-  for (int64_t b = lo; b < hi; b += 32) {
-    const int64_t i = b + lane;
-    int e = -1;
-    if (i < hi) {
-      e = __ldg(p.ids + i);
-      if (e < 0 || e >= E) {
-        report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(e));
-        e = -1;
+  constexpr int NREG = ITERS > 0 ? ITERS : 1;
+  int held[NREG];
+  if constexpr (ITERS > 0) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int64_t i = lo + it * 32 + lane;
+      held[it] = (i < hi) ? __ldg(p.ids + i) : -1;
+    }
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int64_t i = lo + it * 32 + lane;
+      if (i < hi && (held[it] < 0 || held[it] >= E)) {
+        report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(held[it]));
+        held[it] = -1;
       }
     }
-    const unsigned grp = __match_any_sync(0xffffffffu, e);
-    if (e >= 0 && lane == (__ffs(grp) - 1)) my[e] += __popc(grp);
-    __syncwarp();
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      if (lo + it * 32 < hi) {
+        const int e = held[it];
+        const unsigned grp = same_expert_lanes(e, p.nbits);
+        if (e >= 0 && lane == (__ffs(grp) - 1)) my[e] += __popc(grp);
+        __syncwarp();
+      }
+    }
+  } else {
+    for (int64_t b = lo; b < hi; b += 32) {
+      const int64_t i = b + lane;
+      int e = -1;
+      if (i < hi) {
+        e = __ldg(p.ids + i);
+        if (e < 0 || e >= E) {
+          report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(e));
+          e = -1;
+        }
+      }
+      const unsigned grp = same_expert_lanes(e, p.nbits);
+      if (e >= 0 && lane == (__ffs(grp) - 1)) my[e] += __popc(grp);
+      __syncwarp();
+    }
   }
   __syncthreads();
 
@@ -308,11 +352,17 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
     cta_tot[e] = run;
   }
   cluster.sync();
+  // gather every CTA's totals (one remote load per thread, all in flight), then reduce locally
+  int* gathered = before + E;  // [C][E]
+  for (int i = threadIdx.x; i < C * E; i += blockDim.x) {
+    const int c = i / E, e = i - c * E;
+    gathered[i] = cluster.map_shared_rank(cta_tot, c)[e];
+  }
+  __syncthreads();
   for (int e = threadIdx.x; e < E; e += blockDim.x) {
     int t = 0, bfr = 0;
     for (int c = 0; c < C; ++c) {
-      const int* remote = cluster.map_shared_rank(cta_tot, c);
-      const int v = remote[e];
+      const int v = gathered[c * E + e];
       if (c < rank) bfr += v;
       t += v;
     }
@@ -347,14 +397,8 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
   __syncthreads();
 
   // pass 2: scatter
-  for (int64_t b = lo; b < hi; b += 32) {
-    const int64_t i = b + lane;
-    int e = -1;
-    if (i < hi) {
-      e = __ldg(p.ids + i);
-      if (e < 0 || e >= E) e = -1;
-    }
-    const unsigned grp = __match_any_sync(0xffffffffu, e);
+  auto place = [&](int64_t i, int e) {
+    const unsigned grp = same_expert_lanes(e, p.nbits);
     int pos = 0;
     if (e >= 0) pos = my[e] + __popc(grp & ((1u << lane) - 1u));
     __syncwarp();
@@ -364,6 +408,21 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
       if (p.inv_pos) p.inv_pos[i] = pos;
     }
     __syncwarp();
+  };
+  if constexpr (ITERS > 0) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it)
+      if (lo + it * 32 < hi) place(lo + it * 32 + lane, held[it]);
+  } else {
+    for (int64_t b = lo; b < hi; b += 32) {
+      const int64_t i = b + lane;
+      int e = -1;
+      if (i < hi) {
+        e = __ldg(p.ids + i);
+        if (e < 0 || e >= E) e = -1;
+      }
+      place(i, e);
+    }
   }
 
   // padding entries, block -> expert table, tails; spread over the cluster
@@ -406,12 +465,16 @@ int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* s
   seg = (seg + 31) / 32 * 32;
   if (seg == 0) seg = 32;
 
-  AlignParams p{topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post, counts, inv_pos, seg};
-  const size_t smem = (static_cast<size_t>(nwarps) * E + 4 * static_cast<size_t>(E) + 1) * sizeof(int);
+  AlignParams p{topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post, counts, inv_pos, seg, 0};
+  while ((1 << p.nbits) < E) ++p.nbits;
+  const size_t smem = (static_cast<size_t>(nwarps) * E + (4 + static_cast<size_t>(C)) * E + 1) * sizeof(int);
   if (smem > 200 * 1024) return FR_ERR_UNSUPPORTED;
+  const int64_t rows_per_warp = seg / 32;
+  void (*kern)(AlignParams) = rows_per_warp <= 4    ? align_cluster_kernel<4>
+                              : rows_per_warp <= 16 ? align_cluster_kernel<16>
+                                                    : align_cluster_kernel<0>;
   if (smem > 48 * 1024)
-    FR_CUDA_OK(cudaFuncSetAttribute(align_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    static_cast<int>(smem)));
+    FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(C);
   cfg.blockDim = dim3(threads);
@@ -424,7 +487,7 @@ int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* s
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FR_CUDA_OK(cudaLaunchKernelEx(&cfg, align_cluster_kernel, p));
+  FR_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
   return FR_OK;
 }
 

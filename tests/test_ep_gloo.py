@@ -1,0 +1,123 @@
+"""Expert-parallel bookkeeping on CPU ranks (gloo, world size 2 and 4): the split sizes,
+the count exchange, the order of received rows and the return path of
+fast_route_b200.parallel.ep, with the CPU oracle standing in for the device kernels.
+The result must equal the single-process oracle layer on the concatenated batch."""
+
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, M, H, I, E, k, skew, out_q, fail_rank):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        import oracle
+        from fast_route_b200 import synth
+        from fast_route_b200.parallel import ep
+
+        group = ep.ExpertParallelGroup(dist.group.WORLD, E)
+        bias = synth.zipf_gate_bias(E, 1.2, 3.0) if skew else None
+        x_all, gate, w1, w2 = synth.moe_inputs(M * world, H, I, E, seed=5, dtype=torch.float32, weight_std=0.1,
+                                               gate_bias=bias)
+        x = x_all[rank * M:(rank + 1) * M]
+        lo, hi = group.local_expert_range()
+        tw, ti, _ = oracle.route_from_hidden(x, gate, k)
+        n = M * k
+        sorted_ids, _, _, counts = oracle.moe_align_block_size(ti, 1, E)
+        counts = torch.from_numpy(counts)
+        if fail_rank == rank:
+            counts = counts.clone()
+            counts[0] += 1                      # an inconsistent histogram must be rejected locally
+        recv_counts = ep.exchange_counts(counts, group)
+        try:
+            ep.validate_counts(counts, n, recv_counts)
+        except RuntimeError as err:
+            out_q.put((rank, "rejected", str(err)))
+            return
+        if fail_rank is not None:
+            out_q.put((rank, "ok-peer", None))
+            return
+        in_splits = ep.send_splits(counts, world)
+        out_splits = recv_counts.sum(dim=1).tolist()
+        order = torch.from_numpy(sorted_ids[:n].astype(np.int64))
+        send_rows = x[order // k].contiguous()
+        send_w = torch.from_numpy(tw).reshape(-1)[order].contiguous()
+        recv_rows = ep.all_to_all_rows(send_rows, in_splits, out_splits, group)
+        recv_w = ep.all_to_all_rows(send_w, in_splits, out_splits, group)
+        row_expert = ep.recv_row_experts(recv_counts)
+        assert row_expert.numel() == recv_rows.shape[0]
+        y = torch.zeros(recv_rows.shape[0], x.shape[1])
+        for e in range(hi - lo):
+            rows = (row_expert == e).nonzero().flatten()
+            if rows.numel():
+                h = oracle.silu_and_mul(recv_rows[rows] @ w1[lo + e].t())
+                y[rows] = (h @ w2[lo + e].t()) * recv_w[rows, None]
+        back = ep.all_to_all_rows(y, out_splits, in_splits, group)
+        inv = np.empty(n, dtype=np.int64)
+        inv[sorted_ids[:n]] = np.arange(n)
+        out = back[torch.from_numpy(inv)].view(M, k, -1).sum(dim=1)
+        ref, _, _ = oracle.moe_layer(x_all, gate, w1, w2, k)
+        err = (out - ref[rank * M:(rank + 1) * M]).abs().max().item()
+        out_q.put((rank, "done", err, in_splits, out_splits))
+    finally:
+        dist.destroy_process_group()
+
+
+def _run(world, M, H, I, E, k, skew=False, fail_rank=None):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, M, H, I, E, k, skew, q, fail_rank))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    return sorted(results)
+
+
+@pytest.mark.parametrize("world,E,k,skew", [(2, 8, 2, False), (4, 8, 2, False), (2, 16, 4, True)])
+def test_ep_exchange_reproduces_single_process_layer(world, E, k, skew):
+    results = _run(world, M=24, H=32, I=48, E=E, k=k, skew=skew)
+    total_in = total_out = 0
+    for rank, tag, err, in_splits, out_splits in results:
+        assert tag == "done" and err < 1e-5, (rank, err)
+        assert sum(in_splits) == 24 * k
+        total_in += sum(in_splits)
+        total_out += sum(out_splits)
+    assert total_in == total_out == world * 24 * k
+
+
+def test_ep_inconsistent_counts_rejected_before_payload():
+    results = _run(2, M=8, H=32, I=16, E=4, k=2, fail_rank=1)
+    tags = {r[0]: r[1] for r in results}
+    assert tags[1] == "rejected" and tags[0] == "ok-peer"
+
+
+def test_ep_helpers():
+    from fast_route_b200.parallel import ep
+    rc = torch.tensor([[2, 0], [1, 3]], dtype=torch.int32)
+    assert ep.recv_row_experts(rc).tolist() == [0, 0, 0, 1, 1, 1]
+    assert ep.send_splits(torch.tensor([1, 2, 3, 4]), 2) == [3, 7]
+    with pytest.raises(RuntimeError):
+        ep.validate_counts(torch.tensor([1, 2]), 4, torch.tensor([[0]]))

@@ -1,0 +1,214 @@
+"""Fused router, grouped GEMMs and the whole layer on the GPU against the CPU oracle.
+
+Tolerances: routing ids / align indices bit-exact; fp16/bf16 layer outputs within max-abs
+2e-2 and mean-rel 1e-2 of the fp32 oracle (the reference's own bar is atol 1e-2 on randn/10
+data, benchmarks/swizzle_moe/perf_test_moe.py:68)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import fast_route_b200 as fr
+import oracle
+from fast_route_b200 import _lib, synth
+from fast_route_b200.ops import fused_moe as fm
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+MAX_ABS, MEAN_REL = 2e-2, 1e-2
+
+
+def bits(a):
+    return np.ascontiguousarray(a).view(np.int32)
+
+
+def check_layer(out, ref):
+    diff = (out.float().cpu() - ref).abs()
+    max_abs = diff.max().item()
+    mean_rel = (diff.mean() / ref.abs().mean()).item()
+    assert max_abs <= MAX_ABS and mean_rel <= MEAN_REL, (max_abs, mean_rel)
+    return max_abs, mean_rel
+
+
+@pytest.mark.parametrize("M,H,E,k,dt", [(256, 512, 8, 2, torch.bfloat16), (300, 1024, 64, 6, torch.bfloat16),
+                                        (128, 256, 128, 8, torch.float16), (1000, 4096, 8, 2, torch.bfloat16),
+                                        (77, 192, 16, 4, torch.float16), (1, 4096, 8, 2, torch.bfloat16),
+                                        (513, 2048, 64, 12, torch.bfloat16), (4096, 1024, 200, 8, torch.float16)])
+def test_fused_route(dev, M, H, E, k, dt):
+    x = synth.randn((M, H), 1, 0).to(dt)
+    wg = synth.randn((E, H), 1, 1, 0.05).to(dt)
+    ref_logits = x.float() @ wg.float().t()
+    for gate in (wg.to(dev).t(), wg.t().contiguous().to(dev)):     # K-major view and row-major [H,E]
+        w, ids, logits = fr.fused_route(x.to(dev), gate, k, return_logits=True)
+        lg = logits.cpu()
+        assert (lg - ref_logits).abs().max().item() < 1e-3 * max(1.0, ref_logits.abs().max().item())
+        ow, oi = oracle.topk_softmax(lg.numpy(), k)
+        assert np.array_equal(ids.cpu().numpy(), oi)             # bit-exact from the device's own logits
+        assert np.array_equal(bits(w.cpu().numpy()), bits(ow))
+        # against the fp32 CPU logits every row whose k-th / (k+1)-th gap is not a near tie agrees
+        so = torch.sort(ref_logits, dim=1, descending=True, stable=True)
+        gaps = (so[0][:, :-1] - so[0][:, 1:])[:, :k].min(dim=1)[0] if E > 1 else torch.ones(M)
+        clear = gaps > 1e-3
+        assert np.array_equal(ids.cpu().numpy()[clear.numpy()], so[1][:, :k].numpy().astype(np.int32)[clear.numpy()])
+
+
+def test_fused_route_reference_golden(dev):
+    """Inputs and outputs of the reference's route_kernel (fp16, Triton interpreter)."""
+    g = np.load(os.path.join(GOLD, "route_kernel.npz"))
+    for case in range(5):
+        M, K, E, k = (int(v) for v in g[f"meta_{case}"])
+        h = torch.from_numpy(g[f"h_{case}"]).to(dev)
+        gate = torch.from_numpy(g[f"g_{case}"]).to(dev)
+        w, ids, logits = fr.fused_route(h, gate, k, return_logits=True)
+        ref_ids, ref_w = g[f"ids_{case}"][:, :k], g[f"w_{case}"][:, :k]
+        lg = torch.sort(logits.cpu(), dim=1, descending=True)[0]
+        clear = ((lg[:, :-1] - lg[:, 1:])[:, :k].min(dim=1)[0] > 1e-4).numpy()
+        assert clear.mean() > 0.9
+        assert np.array_equal(ids.cpu().numpy()[clear], ref_ids[clear])
+        np.testing.assert_allclose(w.cpu().numpy()[clear], ref_w[clear], atol=1e-4)   # reference bar: 1e-2
+
+
+def test_fused_route_reference_style_buffers(dev):
+    """fp16 weights / int64 ids [M,E] buffers as in fast_route/tests/test_route.py:29-33."""
+    M, K, E, k = 512, 4096, 16, 4
+    h = (synth.randn((M, K), 2, 0) / 10).half().to(dev)
+    gate = (synth.randn((K, E), 2, 1) / 10).half().to(dev)
+    tw = torch.empty(M, E, dtype=torch.float16, device=dev)
+    ti = torch.empty(M, E, dtype=torch.int64, device=dev)
+    w, ids = fr.fused_route(h, gate, k, tw, ti)
+    assert w.data_ptr() == tw.data_ptr() and w.shape == (M, k) and w.stride() == (E, 1)
+    score = torch.softmax(h.float() @ gate.float(), dim=-1)
+    rw, ri = torch.topk(score, k)
+    rw = rw / rw.sum(-1, keepdim=True)
+    torch.testing.assert_close(w.float(), rw, atol=1e-2, rtol=0)
+
+
+def small_cases():
+    return [(64, 256, 256, 4, 2, torch.bfloat16), (300, 512, 384, 8, 2, torch.bfloat16),
+            (1000, 256, 640, 16, 4, torch.float16), (5, 512, 1024, 8, 2, torch.bfloat16),
+            (1, 512, 1024, 8, 2, torch.bfloat16), (129, 264, 136, 3, 3, torch.bfloat16),
+            (2048, 512, 256, 64, 6, torch.bfloat16), (16, 1024, 2048, 8, 2, torch.float16)]
+
+
+@pytest.mark.parametrize("M,H,I,E,k,dt", small_cases())
+def test_layer_vs_oracle(dev, M, H, I, E, k, dt):
+    x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=2, dtype=dt, weight_std=0.05)
+    out, tw, ti = fr.fused_moe(x.to(dev), gate.to(dev), w1.to(dev), w2.to(dev), k, return_routing=True)
+    ref, _, _ = oracle.moe_layer(x, gate, w1, w2, k, routing=(tw.cpu(), ti.cpu()))
+    check_layer(out, ref)
+    # determinism: a second call gives the same bits
+    out2 = fr.fused_moe(x.to(dev), gate.to(dev), w1.to(dev), w2.to(dev), k)
+    assert torch.equal(out, out2)
+
+
+def test_layer_reference_cpu_case(dev):
+    """M=256, H=1024, I=2048, E=8, top-2, seed 0 (bf16 on the GPU, fp32 oracle): routing equals the
+    oracle's on every row, output within tolerance of the oracle and of the stored reference sample."""
+    g = np.load(os.path.join(GOLD, "torch_moe.npz"))
+    x, gate, w1, w2 = synth.moe_inputs(256, 1024, 2048, 8, seed=0, dtype=torch.bfloat16)
+    out, tw, ti = fr.fused_moe(x.to(dev), gate.to(dev), w1.to(dev), w2.to(dev), 2, return_routing=True)
+    ref, ow, oi = oracle.moe_layer(x, gate, w1, w2, 2)
+    agree = (ti.cpu().numpy() == oi).all(1)
+    assert agree.mean() > 0.99
+    ref_same, _, _ = oracle.moe_layer(x, gate, w1, w2, 2, routing=(tw.cpu(), ti.cpu()))
+    check_layer(out, ref_same)
+    # fp32 reference output on the unrounded inputs: bf16 rounding of inputs is inside the tolerance too
+    sample = out.float().cpu()[::8, ::16].numpy()
+    rows = agree[::8]
+    assert np.abs(sample[rows] - g["c1_out_sample"][rows]).max() <= MAX_ABS
+
+
+def test_layer_inplace_and_fp16_and_strided_gate(dev):
+    M, H, I, E, k = 100, 256, 384, 8, 2
+    x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=4, dtype=torch.float16, weight_std=0.05)
+    xd = x.to(dev)
+    ref_out = fr.fused_moe(xd.clone(), gate.to(dev), w1.to(dev), w2.to(dev), k)
+    got = fr.fused_moe(xd, gate.to(dev), w1.to(dev), w2.to(dev), k, inplace=True)
+    assert got.data_ptr() == xd.data_ptr() and torch.equal(got, ref_out)
+    out2 = fr.fused_moe(x.to(dev), gate.contiguous().to(dev), w1.to(dev), w2.to(dev), k)   # row-major [H,E]
+    assert torch.equal(out2, ref_out)
+
+
+def test_layer_skewed_routing_with_empty_experts(dev):
+    """Fine-grained layer with a Zipf gate bias (reduced widths, full expert count and top-6)."""
+    M, H, I, E, k = 2048, 512, 256, 64, 6
+    bias = synth.zipf_gate_bias(E, 1.2, 3.0)
+    x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=6, dtype=torch.bfloat16, weight_std=0.05, gate_bias=bias)
+    out, tw, ti = fr.fused_moe(x.to(dev), gate.to(dev), w1.to(dev), w2.to(dev), k, return_routing=True)
+    counts = np.bincount(ti.cpu().numpy().ravel(), minlength=E)
+    assert (counts == 0).any() and counts.max() > 8 * counts.mean()
+    ref, _, _ = oracle.moe_layer(x, gate, w1, w2, k, routing=(tw.cpu(), ti.cpu()))
+    check_layer(out, ref)
+
+
+def test_building_blocks_through_the_operator_surface(dev):
+    """route -> align -> permute -> gemm1 -> gemm2 -> combine called one by one, with split-K
+    forced on, equals the single-call layer bit for bit where the path is the same."""
+    M, H, I, E, k = 48, 512, 768, 8, 2
+    x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=8, dtype=torch.bfloat16, weight_std=0.05)
+    xd, gd, w1d, w2d = x.to(dev), gate.to(dev), w1.to(dev), w2.to(dev)
+    tw, ti = fr.fused_route(xd, gd, k)
+    s, e, npost, cnt, inv = fm.moe_align_block_size(ti, 128, E, return_extra=True)
+    n = M * k
+    rows = (n + min(n, E) * 127 + 127) // 128 * 128
+    a = fm.permute_rows(xd, s, npost, k, max_rows=rows)
+    ref, _, _ = oracle.moe_layer(x, gate, w1, w2, k, routing=(tw.cpu(), ti.cpu()))
+    outs = []
+    for split in (1, 2, 3):
+        act = fm.gemm1_silu(a, w1d, e, npost, s, n, split_k=split)
+        y = fm.gemm2(act, w2d, e, npost, s, tw, n, split_k=split)
+        out = fm.combine(y, inv, M, k)
+        check_layer(out, ref)
+        outs.append(out)
+    assert (outs[0].float() - outs[1].float()).abs().max().item() < 1e-2
+
+
+def test_invoke_fused_moe_kernel_reference_signature(dev):
+    """The reference's three-step tail (ops/fused_moe.py:178-214 used as in layers/stable_route.py:85-102)."""
+    M, H, I, E, k = 64, 256, 128, 4, 2
+    x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=9, dtype=torch.float16, weight_std=0.05)
+    xd, w1d, w2d = x.to(dev), w1.to(dev), w2.to(dev)
+    tw, ti = fr.fused_route(xd, gate.to(dev), k)
+    s, e, npost = fr.moe_align_block_size(ti, 128, E)
+    c1 = torch.zeros(M, k, 2 * I, dtype=x.dtype, device=dev)
+    fr.invoke_fused_moe_kernel(xd, w1d, c1, tw, ti, s, e, npost, False, k, {"BLOCK_SIZE_M": 128})
+    c2 = (torch.nn.functional.silu(c1.float()[..., :I]) * c1.float()[..., I:]).to(x.dtype).view(-1, I)
+    c3 = torch.zeros(M, k, H, dtype=x.dtype, device=dev)
+    fr.invoke_fused_moe_kernel(c2, w2d, c3, tw, ti, s, e, npost, True, 1)
+    out = c3.float().sum(1)
+    ref, _, _ = oracle.moe_layer(x, gate, w1, w2, k, routing=(tw.cpu(), ti.cpu()))
+    check_layer(out, ref)
+
+
+def test_mixtral_shape_full_size_properties(dev):
+    """Full benchmark shape (H=4096, I=14336, E=8, top-2, bf16) at M=4096 and at the small-batch
+    sizes: sampled token rows against a direct fp32 evaluation on the device, and row independence
+    (a token's output does not depend on which batch it is in)."""
+    H, I, E, k = 4096, 14336, 8, 2
+    g = torch.Generator(device=dev).manual_seed(0)
+    w1 = torch.randn(E, 2 * I, H, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
+    w2 = torch.randn(E, H, I, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
+    wg = torch.randn(E, H, device=dev, dtype=torch.bfloat16, generator=g) * 0.02
+    x = torch.randn(4096, H, device=dev, dtype=torch.bfloat16, generator=g)
+    out, tw, ti = fr.fused_moe(x, wg.t(), w1, w2, k, return_routing=True)
+    rows = list(range(0, 4096, 512))
+    ref = torch.zeros(len(rows), H, device=dev)
+    for i, r in enumerate(rows):
+        for j in range(k):
+            ex = int(ti[r, j])
+            h1 = w1[ex].float() @ x[r].float()
+            a = torch.nn.functional.silu(h1[:I]) * h1[I:]
+            ref[i] += tw[r, j] * (w2[ex].float() @ a)
+    # At this shape |out| reaches ~8, where one bf16 ulp is 0.031: the absolute bound gets one bf16
+    # ulp of the reference value added (the output itself is stored in bf16); mean-rel is unchanged.
+    diff = (out[rows].float() - ref).abs()
+    assert (diff <= MAX_ABS + ref.abs() * 2.0 ** -7).all()
+    assert (diff.mean() / ref.abs().mean()).item() <= MEAN_REL
+    for m in (1, 4, 16, 64):            # split-K / small-batch path, same tokens
+        small = fr.fused_moe(x[:m].contiguous(), wg.t(), w1, w2, k)
+        d = (small.float() - out[:m].float()).abs()
+        assert (d <= MAX_ABS + out[:m].float().abs() * 2.0 ** -7).all()
+    assert torch.isfinite(out.float()).all()
+    _lib.raise_on_device_error()

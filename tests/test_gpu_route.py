@@ -1,0 +1,150 @@
+"""Router from logits and the align stage on the GPU, bit-exact against the CPU oracle.
+Shapes follow the reference's tests (fast_route/tests/test_argsort.py:101-145,
+test_route.py:12-77) and the routing microbenchmark (16384 tokens, E in {8,64,128},
+top-k in {2,6,8}, block 64, 5 % rows with exact duplicates)."""
+
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from fast_route_b200 import synth
+from fast_route_b200.ops import fused_moe as fm
+from fast_route_b200.ops import stable_route as sr
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def bits(a):
+    return np.ascontiguousarray(a).view(np.int32)
+
+
+@pytest.mark.parametrize("E,k", [(8, 2), (64, 6), (128, 8), (8, 8), (64, 2), (128, 2)])
+def test_routing_microbench_bit_exact(dev, E, k):
+    M, bs = 16384, 64
+    logits = synth.routing_logits(M, E, k, seed=0, dtype=torch.float16, dup_frac=0.05)
+    w, ids = sr.route_from_logits(logits.to(dev), k)
+    s, e, npost = fm.moe_align_block_size(ids, bs, E)
+    ow, oi = oracle.topk_softmax(logits, k)
+    os_, oe, on, _ = oracle.moe_align_block_size(oi, bs, E)
+    assert np.array_equal(ids.cpu().numpy(), oi)
+    assert np.array_equal(bits(w.cpu().numpy()), bits(ow))
+    assert int(npost.item()) == int(on[0])
+    assert np.array_equal(s.cpu().numpy(), os_)
+    nb = int(on[0]) // bs
+    assert np.array_equal(e.cpu().numpy()[:nb], oe[:nb])
+    # softmax weights are also close to the library softmax (report-level check)
+    wt = torch.softmax(torch.sort(logits.float(), descending=True, stable=True)[0][:, :k], -1).numpy()
+    assert np.abs(w.cpu().numpy() - wt).max() < 5e-7
+
+
+@pytest.mark.parametrize("E", [1, 2, 3, 5, 8, 9, 16, 31, 64, 100, 128, 200, 256, 300])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_topk_shapes_and_dtypes(dev, E, dt):
+    for k in sorted({1, min(2, E), min(8, E), min(12, E), E if E <= 16 else 1}):
+        for M in (1, 33, 1000):
+            logits = synth.routing_logits(M, E, k, seed=E * 7 + k, dtype=dt, dup_frac=0.3)
+            w, ids = sr.route_from_logits(logits.to(dev), k)
+            ow, oi = oracle.topk_softmax(logits, k)
+            assert np.array_equal(ids.cpu().numpy(), oi), (E, k, M)
+            assert np.array_equal(bits(w.cpu().numpy()), bits(ow)), (E, k, M)
+
+
+def test_stable_argsort_golden_vectors(dev):
+    """The reference's own bitonic argsort outputs (ties included) for full-width ordering."""
+    g = np.load(os.path.join(GOLD, "stable_argsort.npz"))
+    for E in (8, 16, 64, 128):
+        for name, dt in (("f16", torch.float16), ("f32", torch.float32)):
+            x = torch.from_numpy(g[f"x_{E}_{name}"]).to(dt)
+            w, ids = sr.route_from_logits(x.to(dev), min(4, E), fill_rest=True)
+            assert np.array_equal(ids.cpu().numpy(), g[f"ids_{E}_{name}"]), (E, name)
+            assert (w[:, min(4, E):] == 0).all()
+
+
+def test_fill_rest_matches_reference_buffers(dev):
+    for E, k in ((8, 2), (64, 6), (128, 8), (300, 12)):
+        logits = synth.routing_logits(500, E, k, seed=3, dtype=torch.float16, dup_frac=0.2)
+        w, ids = sr.route_from_logits(logits.to(dev), k, fill_rest=True)
+        ow, oi = oracle.full_argsort_fill(logits, k)
+        assert np.array_equal(ids.cpu().numpy(), oi)
+        assert np.array_equal(bits(w.cpu().numpy()), bits(ow))
+
+
+def test_strided_logits_and_all_equal_rows(dev):
+    base = synth.routing_logits(257, 64, 4, seed=5, dtype=torch.float16).to(dev)
+    view = base.t().contiguous().t()          # column-major storage
+    assert view.stride(1) != 1
+    w, ids = sr.route_from_logits(view, 4)
+    ow, oi = oracle.topk_softmax(base.cpu(), 4)
+    assert np.array_equal(ids.cpu().numpy(), oi) and np.array_equal(bits(w.cpu().numpy()), bits(ow))
+    flat = torch.zeros(10, 16, dtype=torch.float16, device=dev)   # every value ties: ids 0..k-1
+    w, ids = sr.route_from_logits(flat, 3)
+    assert ids.cpu().tolist() == [[0, 1, 2]] * 10
+    assert np.array_equal(bits(w.cpu().numpy()), bits(oracle.topk_softmax(flat.cpu(), 3)[0]))
+
+
+def test_no_renormalize_matches_softmax_over_all_experts(dev):
+    logits = synth.routing_logits(300, 64, 6, seed=9, dtype=torch.float32)
+    w, ids = sr.route_from_logits(logits.to(dev), 6, renormalize=False)
+    p = torch.softmax(logits, -1)
+    so, si = torch.sort(logits, descending=True, stable=True)
+    assert np.array_equal(ids.cpu().numpy(), si[:, :6].numpy().astype(np.int32))
+    np.testing.assert_allclose(w.cpu().numpy(), p.gather(1, si[:, :6]).numpy(), atol=1e-6)
+
+
+def test_align_docstring_example(dev):
+    ids = torch.tensor([[2, 3, 4], [1, 2, 4], [1, 3, 4], [1, 2, 3]], dtype=torch.int32) - 1
+    s, e, n = fm.moe_align_block_size(ids.to(dev), 4, 4)
+    assert s.cpu().tolist()[:16] == [3, 6, 9, 12, 0, 4, 10, 12, 1, 7, 11, 12, 2, 5, 8, 12]
+    assert e.cpu().tolist()[:4] == [0, 1, 2, 3] and int(n.item()) == 16
+
+
+@pytest.mark.parametrize("M,k,E,bs", [(1, 1, 1, 1), (1, 2, 8, 128), (3, 2, 8, 128), (100, 2, 8, 128),
+                                      (4096, 2, 8, 128), (16384, 2, 8, 64), (16384, 8, 128, 64),
+                                      (16384, 6, 64, 64), (8192, 6, 64, 128), (33, 1, 600, 16),
+                                      (70000, 2, 8, 128), (1000, 4, 1500, 8), (0, 2, 8, 128)])
+def test_align_matches_oracle(dev, M, k, E, bs):
+    g = torch.Generator().manual_seed(M + E)
+    ids = torch.randint(0, E, (M, k), generator=g, dtype=torch.int32)
+    if E >= 8:
+        ids[ids == 5] = 2      # an expert that receives nothing
+    for _ in range(2):         # twice: the result must not depend on scheduling
+        s, e, npost, cnt, inv = fm.moe_align_block_size(ids.to(dev), bs, E, return_extra=True)
+        os_, oe, on, oc = oracle.moe_align_block_size(ids, bs, E)
+        nb = int(on[0]) // bs
+        assert int(npost.item()) == int(on[0])
+        assert np.array_equal(s.cpu().numpy(), os_)
+        assert np.array_equal(e.cpu().numpy()[:nb], oe[:nb])
+        assert (e.cpu().numpy()[nb:] == -1).all()
+        assert np.array_equal(cnt.cpu().numpy(), oc)
+        if M:
+            assert np.array_equal(os_[inv.cpu().numpy()], np.arange(M * k))
+
+
+def test_align_skewed_and_single_expert(dev):
+    M, k, E = 8192, 6, 64
+    bias = synth.zipf_gate_bias(E, 1.2, 3.0)
+    logits = torch.randn(M, E, generator=torch.Generator().manual_seed(1)) + bias
+    _, ids = sr.route_from_logits(logits.to(dev), k)
+    s, e, npost, cnt, _ = fm.moe_align_block_size(ids, 128, E, return_extra=True)
+    os_, oe, on, oc = oracle.moe_align_block_size(ids.cpu(), 128, E)
+    assert np.array_equal(s.cpu().numpy(), os_) and np.array_equal(cnt.cpu().numpy(), oc)
+    assert (oc == 0).any() and oc.max() > 8 * oc.mean()
+    one = torch.full((5000, 1), 3, dtype=torch.int32)
+    s, e, npost = fm.moe_align_block_size(one.to(dev), 128, 8)
+    assert np.array_equal(s.cpu().numpy(), oracle.moe_align_block_size(one, 128, 8)[0])
+
+
+@pytest.mark.reads_status
+def test_out_of_range_expert_id_is_reported_not_trapped(dev):
+    from fast_route_b200 import _lib
+    _lib.device_status()
+    ids = torch.tensor([[0, 1], [9, 1], [2, -1]], dtype=torch.int32, device=dev)
+    s, e, npost = fm.moe_align_block_size(ids, 4, 4)
+    code, detail, _, count = _lib.device_status()
+    assert code == 2 and count == 2
+    assert int(npost.item()) == 12         # the three valid experts 0,1,2 still get their blocks
+    assert _lib.device_status()[0] == 0    # reading clears
