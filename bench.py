@@ -246,10 +246,12 @@ def routing_latency(fr, synth, dev):
         e = torch.empty(n + E, dtype=torch.int32, device=dev)
         npost = torch.empty(1, dtype=torch.int32, device=dev)
 
+        ws = torch.zeros(lib.fr_align_workspace_bytes(E), dtype=torch.uint8, device=dev)   # zeroed once
+
         def call():
             rc = lib.fr_route_align(_lib.ptr(lg), 0, M, E, lg.stride(0), 1, k, _lib.ptr(w), _lib.ptr(ids), bs,
-                                    _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(), _lib.ptr(npost),
-                                    _lib.stream_ptr(dev))
+                                    _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(), _lib.ptr(npost), _lib.ptr(ws),
+                                    ws.numel(), _lib.stream_ptr(dev))
             assert rc == 0, rc
         med, _ = cuda_time_ms(call, 50, 5)
         g = torch.cuda.CUDAGraph()
@@ -264,7 +266,7 @@ def routing_latency(fr, synth, dev):
 
         def call_align():
             rc = lib.fr_align(_lib.ptr(ids), n, E, bs, _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(), _lib.ptr(npost),
-                              None, None, _lib.stream_ptr(dev))
+                              None, None, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
             assert rc == 0, rc
         parts = []
         for fn in (call_topk, call_align):

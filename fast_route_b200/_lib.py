@@ -28,8 +28,9 @@ SIGNATURES = {
     "fr_error_string": (c_char_p, [_I]),
     "fr_check_status": (_I, [_P]),
     "fr_topk_softmax": (_I, [_P, _I, _L, _I, _L, _L, _I, _I, _P, _L, _P, _L, _I, _P]),
-    "fr_align": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _P, _P]),
-    "fr_route_align": (_I, [_P, _I, _L, _I, _L, _L, _I, _P, _P, _I, _P, _L, _P, _L, _P, _P]),
+    "fr_align_workspace_bytes": (_Z, [_I]),
+    "fr_align": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _P, _P, _Z, _P]),
+    "fr_route_align": (_I, [_P, _I, _L, _I, _L, _L, _I, _P, _P, _I, _P, _L, _P, _L, _P, _P, _Z, _P]),
     "fr_route_fused_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fr_route_fused": (_I, [_P, _I, _L, _I, _L, _P, _L, _L, _I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "fr_permute_rows": (_I, [_P, _I, _I, _L, _P, _P, _L, _I, _L, _P, _L, _P]),
@@ -116,11 +117,12 @@ _workspaces: dict = {}
 
 
 def workspace(nbytes: int, device, tag: str = "layer") -> torch.Tensor:
-    """A cached, 1024-byte aligned byte buffer per (device, stream, tag); grows on demand."""
+    """A cached, 1024-byte aligned byte buffer per (device, stream, tag); grows on demand.
+    New buffers are zero-filled once (the align stage keeps its grid-barrier words there)."""
     key = (torch.device(device).index, torch.cuda.current_stream(device).cuda_stream, tag)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < nbytes + 1024:
-        buf = torch.empty(int(nbytes * 1.0) + 1024, dtype=torch.uint8, device=device)
+        buf = torch.zeros(int(nbytes) + 1024, dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     off = (-buf.data_ptr()) % 1024
     return buf[off:off + max(nbytes, 1)]

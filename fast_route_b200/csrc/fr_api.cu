@@ -10,7 +10,8 @@ int topk_softmax_dispatch(const void* logits, int dtype, int64_t M, int E, int64
                           int64_t id_stride, int fill_rest, cudaStream_t st);
 int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                    int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                   int32_t* inv_pos, cudaStream_t st);
+                   int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st);
+size_t coop_workspace_bytes(int E);
 int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, int dtype, int64_t max_rows,
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
@@ -22,6 +23,11 @@ int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx
                          int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
                          int32_t* ids, float* logits_out, cudaStream_t st);
 int choose_split_k(int64_t est_tiles, int KB, int sm_count);
+int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t stride_m, int64_t stride_e,
+                              int topk, float* weights, int32_t* ids_out, const int32_t* ids_in, int64_t n, int E,
+                              int bs, int32_t* sorted_ids, int64_t sorted_len, int32_t* expert_ids,
+                              int64_t expert_ids_len, int32_t* num_post, int32_t* counts, int32_t* inv_pos,
+                              void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 constexpr int kBlockM = FR_GEMM_BLOCK_M;
 constexpr int kTileN = 256;
@@ -292,6 +298,8 @@ struct ExpertWs {
   int32_t *sorted, *expert_ids, *num_post, *inv_pos;
   uint16_t *a_sorted, *act, *y_sorted;
   void* split;
+  void* align_ws;
+  size_t align_ws_bytes;
   int64_t rows, sorted_len, expert_ids_len;
   SplitPlan sp;
 };
@@ -304,6 +312,8 @@ static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
   w.expert_ids = c.take<int32_t>(w.expert_ids_len);
   w.num_post = c.take<int32_t>(4);
   w.inv_pos = c.take<int32_t>(n);
+  w.align_ws_bytes = coop_workspace_bytes(E);
+  w.align_ws = c.take<uint8_t>(w.align_ws_bytes);
   w.a_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
   w.act = c.take<uint16_t>(static_cast<size_t>(w.rows) * I);
   w.y_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
@@ -319,7 +329,7 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
                         int64_t ld_out, const ExpertWs& w, cudaStream_t st) {
   const int64_t n = M * topk;
   int rc = align_dispatch(ids, n, E, kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len, w.num_post,
-                          nullptr, w.inv_pos, st);
+                          nullptr, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
   if (rc) return rc;
   const int row_v = H / 8;
   permute_rows_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
@@ -382,21 +392,36 @@ int fr_topk_softmax(const void* logits, int dtype, int64_t M, int E, int64_t str
                                id_stride, fill_rest, static_cast<cudaStream_t>(stream));
 }
 
+size_t fr_align_workspace_bytes(int E) { return E > 0 ? coop_workspace_bytes(E) : 0; }
+
 int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids, int64_t sorted_len,
              int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad, int32_t* counts,
-             int32_t* inv_pos, void* stream) {
+             int32_t* inv_pos, void* workspace, size_t workspace_bytes, void* stream) {
   return align_dispatch(topk_ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
-                        num_tokens_post_pad, counts, inv_pos, static_cast<cudaStream_t>(stream));
+                        num_tokens_post_pad, counts, inv_pos, workspace, workspace_bytes,
+                        static_cast<cudaStream_t>(stream));
 }
 
 int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e, int topk,
                    float* weights, int32_t* ids, int block_size, int32_t* sorted_ids, int64_t sorted_len,
-                   int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad, void* stream) {
+                   int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad, void* workspace,
+                   size_t workspace_bytes, void* stream) {
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = topk_softmax_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, 1, weights, topk, ids, topk, 0, st);
+  if (!logits || !weights || !ids || !sorted_ids || !expert_ids || !num_tokens_post_pad || M < 0 || E <= 0 ||
+      topk <= 0 || topk > E || block_size <= 0)
+    return FR_ERR_ARG;
+  const int64_t n = M * topk;
+  if (sorted_len < n + static_cast<int64_t>(E) * (block_size - 1) ||
+      expert_ids_len < (n + static_cast<int64_t>(E) * (block_size - 1)) / block_size)
+    return FR_ERR_ARG;
+  int rc = route_align_coop_dispatch(logits, dtype, M, stride_m, stride_e, topk, weights, ids, nullptr, n, E,
+                                     block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
+                                     num_tokens_post_pad, nullptr, nullptr, workspace, workspace_bytes, st);
+  if (rc != FR_ERR_UNSUPPORTED) return rc;
+  rc = topk_softmax_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, 1, weights, topk, ids, topk, 0, st);
   if (rc) return rc;
-  return align_dispatch(ids, M * topk, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
-                        num_tokens_post_pad, nullptr, nullptr, st);
+  return align_dispatch(ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
+                        num_tokens_post_pad, nullptr, nullptr, workspace, workspace_bytes, st);
 }
 
 size_t fr_route_fused_workspace_bytes(int64_t M, int H, int E, int topk) {

@@ -21,6 +21,16 @@ namespace fr {
 // ----------------------------------------------------------------------------------
 constexpr int KMAX = 8;
 
+// packed-key top-k for 16-bit logits and the cooperative route+align kernel (fr_route_coop.cu)
+template <typename T>
+int launch_topk16(const void* logits, int64_t M, int E, int64_t stride_m, int64_t stride_e, int k, float* weights,
+                  int64_t w_stride, int32_t* ids, int64_t id_stride, cudaStream_t st);
+int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t stride_m, int64_t stride_e,
+                              int topk, float* weights, int32_t* ids_out, const int32_t* ids_in, int64_t n, int E,
+                              int bs, int32_t* sorted_ids, int64_t sorted_len, int32_t* expert_ids,
+                              int64_t expert_ids_len, int32_t* num_post, int32_t* counts, int32_t* inv_pos,
+                              void* workspace, size_t workspace_bytes, cudaStream_t st);
+
 __device__ __forceinline__ bool beats(float v, int c, float bv, int bc) {
   return (v > bv) || (v == bv && c < bc);
 }
@@ -184,6 +194,10 @@ static int launch_topk(const void* logits, int64_t M, int E, int64_t stride_m, i
                        int fill_rest, cudaStream_t st) {
   const T* lp = static_cast<const T*>(logits);
   const bool reg_path = !fill_rest && k <= KMAX && E <= 256;
+  if constexpr (sizeof(T) == 2) {
+    if (reg_path && renormalize)
+      return launch_topk16<T>(logits, M, E, stride_m, stride_e, k, weights, w_stride, ids, id_stride, st);
+  }
   if (reg_path) {
     const int threads = 256;
 #define FR_LAUNCH_TOPK(L_, VPL_)                                                                            \
@@ -446,13 +460,21 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
 
 int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                    int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                   int32_t* inv_pos, cudaStream_t st) {
+                   int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!sorted_ids || !expert_ids || !num_post || n < 0 || E <= 0 || bs <= 0) return FR_ERR_ARG;
   if (n > 0 && !topk_ids) return FR_ERR_ARG;
   if (n >= (1ll << 30) || E > 2048) return FR_ERR_UNSUPPORTED;
   // every possible layout must fit: the reference allocates exactly these sizes
   if (sorted_len < n + static_cast<int64_t>(E) * (bs - 1)) return FR_ERR_ARG;
   if (expert_ids_len < (n + static_cast<int64_t>(E) * (bs - 1)) / bs) return FR_ERR_ARG;
+
+  // many assignments and a scratch buffer: spread over the whole GPU (one cooperative launch)
+  {
+    const int rc = route_align_coop_dispatch(nullptr, 0, 0, 0, 0, 1, nullptr, nullptr, topk_ids, n, E, bs, sorted_ids,
+                                             sorted_len, expert_ids, expert_ids_len, num_post, counts, inv_pos,
+                                             workspace, workspace_bytes, st);
+    if (rc != FR_ERR_UNSUPPORTED) return rc;
+  }
 
   int threads = 1024;
   if (E > 1024) threads = 256;

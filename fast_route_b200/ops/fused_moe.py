@@ -30,9 +30,11 @@ def moe_align_block_size(topk_ids: torch.Tensor, block_size: int, num_experts: i
     num_post = torch.empty(1, dtype=torch.int32, device=dev)
     counts = torch.empty(num_experts, dtype=torch.int32, device=dev) if return_extra else None
     inv = torch.empty(max(n, 1), dtype=torch.int32, device=dev) if return_extra else None
-    rc = _lib.load().fr_align(_lib.ptr(ids), n, num_experts, block_size, _lib.ptr(sorted_ids), sorted_ids.numel(),
-                              _lib.ptr(expert_ids), expert_ids.numel(), _lib.ptr(num_post), _lib.ptr(counts),
-                              _lib.ptr(inv), _lib.stream_ptr(dev))
+    lib = _lib.load()
+    ws = _lib.workspace(lib.fr_align_workspace_bytes(num_experts), dev, "align")
+    rc = lib.fr_align(_lib.ptr(ids), n, num_experts, block_size, _lib.ptr(sorted_ids), sorted_ids.numel(),
+                      _lib.ptr(expert_ids), expert_ids.numel(), _lib.ptr(num_post), _lib.ptr(counts),
+                      _lib.ptr(inv), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
     _lib.check(rc, "fr_align")
     if return_extra:
         return sorted_ids, expert_ids, num_post, counts, inv[:n]

@@ -65,17 +65,25 @@ int fr_topk_softmax(const void* logits, int dtype, int64_t M, int E, int64_t str
  * op it calls plus the fill_ of the wrapper).  sorted_ids has sorted_len entries
  * (>= n + E*(block_size-1)), expert_ids has expert_ids_len entries; entries past the valid
  * prefix are set to n / -1.  Optional outputs (may be NULL): counts[E] tokens per expert,
- * inv_pos[n] position of every flat assignment in sorted_ids. */
+ * inv_pos[n] position of every flat assignment in sorted_ids.
+ * workspace (may be NULL): fr_align_workspace_bytes(E) bytes of scratch, 16-byte aligned, that
+ * lets batches of >= 8192 assignments run as one cooperative launch over all SMs instead of one
+ * 8-CTA cluster.  Its first 8 bytes are a grid-barrier word pair: ZERO THE BUFFER ONCE before
+ * its first use (and again after fr_check_status has reported an expired wait); completed calls
+ * leave it ready for the next one.  One workspace serves one stream at a time. */
+size_t fr_align_workspace_bytes(int E);
 int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids,
              int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad,
-             int32_t* counts, int32_t* inv_pos, void* stream);
+             int32_t* counts, int32_t* inv_pos, void* workspace, size_t workspace_bytes, void* stream);
 
 /* fr_topk_softmax followed by fr_align on its compact [M,topk] ids: the routing/align
- * latency path (logits -> the five routing outputs). */
+ * latency path (logits -> the five routing outputs).  With 16-bit logits, topk <= 8, E <= 256,
+ * >= 8192 assignments and a workspace (same contract as fr_align) both stages run inside ONE
+ * cooperative kernel; otherwise as two launches.  Outputs are identical either way. */
 int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e,
                    int topk, float* weights, int32_t* ids, int block_size, int32_t* sorted_ids,
                    int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len,
-                   int32_t* num_tokens_post_pad, void* stream);
+                   int32_t* num_tokens_post_pad, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Fused router: logits = X[M,H] . G[H,E] on the tensor cores with the top-k / softmax
  * epilogue in registers.  Stands in for fused_route + route_kernel,
@@ -135,7 +143,8 @@ int fr_combine(const void* y, int64_t ld_y, int dtype, const int32_t* inv_pos, i
  * Stands in for fused_moe, fast_route/fast_route/layers/stable_route.py:10-102.
  * x[M,H], gate as in fr_route_fused, w1[E,2I,H], w2[E,H,I], out[M,H] (may alias x: the
  * reference's inplace=True).  topk_weights_out / topk_ids_out (may be NULL) receive the
- * compact routing.  The workspace holds every intermediate. */
+ * compact routing.  The workspace (1024-byte aligned) holds every intermediate; zero it once
+ * before its first use (it contains the align stage's grid-barrier words, see fr_align). */
 size_t fr_moe_workspace_bytes(int64_t M, int H, int I, int E, int topk);
 int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t gate_stride_e, const void* w1,
                  const void* w2, int dtype, int64_t M, int H, int I, int E, int topk, int renormalize, void* out,
@@ -146,7 +155,7 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
  * fr_moe_experts: the expert part of the layer for rows that already carry an expert id
  * (tokens received from other ranks): align by local expert -> permute -> GEMM1+SiLU ->
  * GEMM2 -> rows returned in the order they came in.  rows[R,H], row_expert[R] in
- * [0, E_local), row_weight[R] (may be NULL), y[R,H]. */
+ * [0, E_local), row_weight[R] (may be NULL), y[R,H].  Workspace contract as fr_moe_layer. */
 size_t fr_moe_experts_workspace_bytes(int64_t R, int H, int I, int E_local);
 int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row_weight, const void* w1,
                    const void* w2, int dtype, int64_t R, int H, int I, int E_local, void* y, void* workspace,

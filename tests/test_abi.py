@@ -55,7 +55,7 @@ def test_workspace_queries_need_no_gpu(lib):
 def test_argument_checks_reject_before_any_launch(lib):
     null = ctypes.c_void_p(None)
     assert lib.fr_topk_softmax(null, 0, 4, 8, 8, 1, 2, 1, null, 2, null, 2, 0, null) == -1
-    assert lib.fr_align(null, 8, 4, 16, null, 100, null, 100, null, null, null, null) == -1
+    assert lib.fr_align(null, 8, 4, 16, null, 100, null, 100, null, null, null, null, 0, null) == -1
     assert lib.fr_moe_layer(null, null, 1, 1, null, null, 1, 4, 64, 64, 4, 2, 1, null, null, null, null, 0, null) == -1
     assert lib.fr_combine(null, 8, 1, null, 4, 2, 64, 128, null, 8, null) == -1
 

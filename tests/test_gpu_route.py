@@ -148,3 +148,41 @@ def test_out_of_range_expert_id_is_reported_not_trapped(dev):
     assert code == 2 and count == 2
     assert int(npost.item()) == 12         # the three valid experts 0,1,2 still get their blocks
     assert _lib.device_status()[0] == 0    # reading clears
+
+
+def _route_align_c_abi(dev, logits, k, bs, with_ws):
+    """fr_route_align through the C ABI; with a workspace it is the single cooperative kernel."""
+    from fast_route_b200 import _lib
+    lib = _lib.load()
+    M, E = logits.shape
+    n = M * k
+    lg = logits.to(dev)
+    w = torch.empty(M, k, dtype=torch.float32, device=dev)
+    ids = torch.empty(M, k, dtype=torch.int32, device=dev)
+    s = torch.empty(n + E * (bs - 1), dtype=torch.int32, device=dev)
+    e = torch.empty(n + E, dtype=torch.int32, device=dev)
+    npost = torch.empty(1, dtype=torch.int32, device=dev)
+    ws = torch.zeros(lib.fr_align_workspace_bytes(E), dtype=torch.uint8, device=dev) if with_ws else None
+    for _ in range(3):      # the workspace must stay reusable call after call
+        rc = lib.fr_route_align(_lib.ptr(lg), _lib.dtype_code(lg.dtype), M, E, lg.stride(0), lg.stride(1), k,
+                                _lib.ptr(w), _lib.ptr(ids), bs, _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(),
+                                _lib.ptr(npost), _lib.ptr(ws), ws.numel() if with_ws else 0, _lib.stream_ptr(dev))
+        assert rc == 0
+    return w.cpu().numpy(), ids.cpu().numpy(), s.cpu().numpy(), e.cpu().numpy(), int(npost.item())
+
+
+@pytest.mark.parametrize("E,k,M,dt", [(8, 2, 16384, torch.float16), (64, 6, 16384, torch.float16),
+                                      (128, 8, 16384, torch.float16), (128, 8, 16384, torch.bfloat16),
+                                      (64, 6, 5000, torch.float16), (100, 4, 9000, torch.bfloat16),
+                                      (256, 8, 3000, torch.float16), (8, 2, 300000, torch.float16),
+                                      (16, 1, 20000, torch.float16)])
+@pytest.mark.parametrize("with_ws", [True, False])
+def test_route_align_fused_entry_point(dev, E, k, M, dt, with_ws):
+    bs = 64
+    logits = synth.routing_logits(M, E, k, seed=21, dtype=dt, dup_frac=0.05)
+    w, ids, s, e, npost = _route_align_c_abi(dev, logits, k, bs, with_ws)
+    ow, oi = oracle.topk_softmax(logits, k)
+    os_, oe, on, _ = oracle.moe_align_block_size(oi, bs, E)
+    assert np.array_equal(ids, oi) and np.array_equal(bits(w), bits(ow))
+    assert npost == int(on[0]) and np.array_equal(s, os_)
+    assert np.array_equal(e[:npost // bs], oe[:npost // bs]) and (e[npost // bs:] == -1).all()
