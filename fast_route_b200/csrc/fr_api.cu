@@ -23,11 +23,6 @@ int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx
                          int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
                          int32_t* ids, float* logits_out, cudaStream_t st);
 int choose_split_k(int64_t est_tiles, int KB, int sm_count);
-int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t stride_m, int64_t stride_e,
-                              int topk, float* weights, int32_t* ids_out, const int32_t* ids_in, int64_t n, int E,
-                              int bs, int32_t* sorted_ids, int64_t sorted_len, int32_t* expert_ids,
-                              int64_t expert_ids_len, int32_t* num_post, int32_t* counts, int32_t* inv_pos,
-                              void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 constexpr int kBlockM = FR_GEMM_BLOCK_M;
 constexpr int kTileN = 256;
@@ -414,11 +409,7 @@ int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stri
   if (sorted_len < n + static_cast<int64_t>(E) * (block_size - 1) ||
       expert_ids_len < (n + static_cast<int64_t>(E) * (block_size - 1)) / block_size)
     return FR_ERR_ARG;
-  int rc = route_align_coop_dispatch(logits, dtype, M, stride_m, stride_e, topk, weights, ids, nullptr, n, E,
-                                     block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
-                                     num_tokens_post_pad, nullptr, nullptr, workspace, workspace_bytes, st);
-  if (rc != FR_ERR_UNSUPPORTED) return rc;
-  rc = topk_softmax_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, 1, weights, topk, ids, topk, 0, st);
+  int rc = topk_softmax_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, 1, weights, topk, ids, topk, 0, st);
   if (rc) return rc;
   return align_dispatch(ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
                         num_tokens_post_pad, nullptr, nullptr, workspace, workspace_bytes, st);

@@ -25,11 +25,9 @@ constexpr int KMAX = 8;
 template <typename T>
 int launch_topk16(const void* logits, int64_t M, int E, int64_t stride_m, int64_t stride_e, int k, float* weights,
                   int64_t w_stride, int32_t* ids, int64_t id_stride, cudaStream_t st);
-int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t stride_m, int64_t stride_e,
-                              int topk, float* weights, int32_t* ids_out, const int32_t* ids_in, int64_t n, int E,
-                              int bs, int32_t* sorted_ids, int64_t sorted_len, int32_t* expert_ids,
-                              int64_t expert_ids_len, int32_t* num_post, int32_t* counts, int32_t* inv_pos,
-                              void* workspace, size_t workspace_bytes, cudaStream_t st);
+int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
+                        int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
+                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st);
 
 __device__ __forceinline__ bool beats(float v, int c, float bv, int bc) {
   return (v > bv) || (v == bv && c < bc);
@@ -470,9 +468,8 @@ int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* s
 
   // many assignments and a scratch buffer: spread over the whole GPU (one cooperative launch)
   {
-    const int rc = route_align_coop_dispatch(nullptr, 0, 0, 0, 0, 1, nullptr, nullptr, topk_ids, n, E, bs, sorted_ids,
-                                             sorted_len, expert_ids, expert_ids_len, num_post, counts, inv_pos,
-                                             workspace, workspace_bytes, st);
+    const int rc = align_coop_dispatch(topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len,
+                                       num_post, counts, inv_pos, workspace, workspace_bytes, st);
     if (rc != FR_ERR_UNSUPPORTED) return rc;
   }
 

@@ -1,6 +1,6 @@
-// Low-latency routing: (1) top-k on packed sortable keys for 16-bit logits, (2) one
-// cooperative kernel that spreads route + align over every SM with a single bounded grid
-// barrier.  Same outputs, bit for bit, as the kernels in fr_route.cu; these exist because the
+// Low-latency routing: (1) top-k on packed sortable keys for 16-bit logits, (2) a
+// cooperative align kernel that spreads the counting sort over every SM with a single
+// bounded grid barrier.  Same outputs, bit for bit, as the kernels in fr_route.cu; these exist because the
 // routing stage moves well under 10 MB and is bound by instruction issue and launch latency,
 // not by HBM (reference stage: route_kernel epilogue, ops/stable_route.py:91-121, followed by
 // moe_align_block_size, ops/fused_moe.py:133-175).
@@ -86,28 +86,35 @@ __device__ __forceinline__ void select_topk(uint32_t (&keys)[8], int k, unsigned
   }
 }
 
-// Softmax over the k winners with the fixed fp32 recipe.  Lane `sub` of the group evaluates
-// the exponentials of slots sub, sub+L, ...; the sequential sum is formed identically by all.
-// Slot j is written by lane j % L.
+// Softmax over the k winners with the fixed fp32 recipe.  Lane `sub` of the group owns the
+// slots sub, sub+L, ...: it evaluates their exponentials, all lanes form the same sequential
+// sum from the exchanged values, and the owner divides and stores its slots (one IEEE division
+// per owned slot; consecutive lanes write consecutive addresses).
 template <typename T, int L>
 __device__ __forceinline__ void write_topk(const uint32_t (&win)[PK], int k, int sub, int lane, unsigned group_mask,
                                            bool row_ok, float* wrow, int32_t* irow, int32_t* sm_ids) {
   const float v0 = key_value<T>(win[0]);
-  float e[PK];
+  constexpr int PER = (PK + L - 1) / L;
+  float e[PK], mine[PER];
+  uint32_t mykey[PER];
 #pragma unroll
   for (int j = 0; j < PK; ++j) e[j] = 0.0f;
-  constexpr int PER = (PK + L - 1) / L;
 #pragma unroll
   for (int r = 0; r < PER; ++r) {
-    const int myj = sub + r * L;
-    uint32_t kk = win[0];
+    mine[r] = 0.0f;
+    mykey[r] = 0;
+    if (r * L < k) {  // uniform over the warp
+      const int myj = sub + r * L;
+      uint32_t kk = win[0];
 #pragma unroll
-    for (int j = 1; j < PK; ++j) kk = (myj == j) ? win[j] : kk;
-    const float mine = exp_recipe(__fsub_rn(key_value<T>(kk), v0));
+      for (int j = 1; j < PK; ++j) kk = (myj == j) ? win[j] : kk;
+      mykey[r] = kk;
+      mine[r] = exp_recipe(__fsub_rn(key_value<T>(kk), v0));
 #pragma unroll
-    for (int j = r * L; j < PK && j < (r + 1) * L; ++j) {
-      const float got = (L > 1) ? __shfl_sync(group_mask, mine, (lane & ~(L - 1)) + (j - r * L)) : mine;
-      if (L > 1 || j == myj) e[j] = got;
+      for (int j = r * L; j < PK && j < (r + 1) * L; ++j) {
+        if (L > 1) e[j] = __shfl_sync(group_mask, mine[r], (lane & ~(L - 1)) + (j - r * L));
+        else e[j] = mine[r];
+      }
     }
   }
   float s = e[0];
@@ -115,12 +122,13 @@ __device__ __forceinline__ void write_topk(const uint32_t (&win)[PK], int k, int
   for (int j = 1; j < PK; ++j)
     if (j < k) s = __fadd_rn(s, e[j]);
 #pragma unroll
-  for (int j = 0; j < PK; ++j) {
-    if (j < k && (j % L) == sub && row_ok) {
-      wrow[j] = __fdiv_rn(e[j], s);
-      const int c = key_col(win[j]);
-      irow[j] = c;
-      if (sm_ids) sm_ids[j] = c;
+  for (int r = 0; r < PER; ++r) {
+    const int myj = sub + r * L;
+    if (r * L < k && myj < k && row_ok) {
+      wrow[myj] = __fdiv_rn(mine[r], s);
+      const int c = key_col(mykey[r]);
+      irow[myj] = c;
+      if (sm_ids) sm_ids[myj] = c;
     }
   }
 }
@@ -232,14 +240,6 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int nbl
 }
 
 struct CoopParams {
-  // optional routing phase (16-bit logits)
-  const void* logits;
-  int64_t M, stride_m, stride_e;
-  int topk;
-  float* weights;
-  int32_t* ids_out;
-  int vec_ok;
-  // align
   const int32_t* ids_in;
   int64_t n;
   int E, bs, nbits;
@@ -253,96 +253,80 @@ struct CoopParams {
   // scratch
   int32_t* hist;          // [gridDim][E]
   unsigned int* barrier;  // [2]
-  int64_t per_block;      // assignments per block (rows_per_block * topk when routing)
-  int64_t rows_per_block;
+  int64_t per_block;      // assignments per block
   int64_t seg;            // assignments per warp, multiple of 32
 };
 
-template <typename T, int L>
-__device__ __forceinline__ void coop_route_phase(const CoopParams& p, int32_t* sids) {
-  const int lane = threadIdx.x & 31;
-  const int sub = threadIdx.x % L;
-  const unsigned group_mask = (L == 32) ? 0xffffffffu : (((1u << L) - 1u) << (lane & ~(L - 1)));
-  const int64_t r0 = static_cast<int64_t>(blockIdx.x) * p.rows_per_block;
-  const int64_t r1 = min(p.M, r0 + p.rows_per_block);
-  const int rows_per_iter = blockDim.x / L;
-  const T* lg = static_cast<const T*>(p.logits);
-  for (int64_t base = r0; base < r1; base += rows_per_iter) {
-    const int64_t row = base + threadIdx.x / L;
-    const bool row_ok = row < r1;
-    const int64_t r = row_ok ? row : (r1 - 1);
-    uint32_t keys[8], win[PK];
-    load_keys<T, L>(lg + r * p.stride_m, p.stride_e, p.E, sub, p.vec_ok != 0, keys);
-    sort8_desc(keys);
-    select_topk<L>(keys, p.topk, group_mask, win);
-    write_topk<T, L>(win, p.topk, sub, lane, group_mask, row_ok, p.weights + r * p.topk, p.ids_out + r * p.topk,
-                     sids + (r - r0) * p.topk);
-  }
-}
-
-template <typename T, int L>
-__global__ void __launch_bounds__(1024) route_align_coop_kernel(const CoopParams p) {
+__global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
   extern __shared__ int csm[];
   const int nwarps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int E = p.E;
+  const int ES = E | 1;            // odd row stride: column reads across warps hit distinct banks
   const int B = gridDim.x;
-  int* cnt = csm;                  // [nwarps][E]
-  int* total = cnt + nwarps * E;   // [E]
-  int* before = total + E;         // [E]
-  int* start = before + E;         // [E+1]
-  int32_t* sids = start + E + 1;   // [per_block] this block's slice of the flat ids
+  int* cnt = csm;                  // [nwarps][ES] per-warp counts, then exclusive prefixes over the warps
+  int* total = cnt + nwarps * ES;  // [E]   totals over the grid
+  int* before = total + E;         // [E]   counts of lower-numbered blocks, later + padded start
+  int* start = before + E;         // [E+1] padded starts
+  int* padded = start + E + 1;     // [E]
+  int32_t* sids = padded + E;      // [per_block] this block's slice of the flat ids
 
   const int64_t lo_blk = static_cast<int64_t>(blockIdx.x) * p.per_block;
   const int64_t hi_blk = min(p.n, lo_blk + p.per_block);
   const int slice = hi_blk > lo_blk ? static_cast<int>(hi_blk - lo_blk) : 0;
-
-  for (int i = threadIdx.x; i < nwarps * E + 2 * E; i += blockDim.x) cnt[i] = 0;  // cnt, total, before
-  if (p.logits) {
-    coop_route_phase<T, L>(p, sids);
-  } else {
-    for (int i = threadIdx.x; i < slice; i += blockDim.x) {
-      int e = __ldg(p.ids_in + lo_blk + i);
-      if (e < 0 || e >= E) {
-        report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(e));
-        e = -1;
-      }
-      sids[i] = e;
+  for (int i = threadIdx.x; i < nwarps * ES + 2 * E; i += blockDim.x) cnt[i] = 0;  // cnt, total, before
+  for (int i = threadIdx.x; i < slice; i += blockDim.x) {
+    int e = __ldg(p.ids_in + lo_blk + i);
+    if (e < 0 || e >= E) {
+      report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(e));
+      e = -1;
     }
+    sids[i] = e;
   }
   __syncthreads();
 
   // pass 1: per-warp counts over the warp's contiguous sub-slice (order of the atomics is irrelevant)
   const int wlo = static_cast<int>(min(static_cast<int64_t>(slice), static_cast<int64_t>(warp) * p.seg));
   const int whi = static_cast<int>(min(static_cast<int64_t>(slice), static_cast<int64_t>(warp + 1) * p.seg));
-  int* my = cnt + warp * E;
+  int* my = cnt + warp * ES;
   for (int i = wlo + lane; i < whi; i += 32) {
     const int e = sids[i];
     if (e >= 0) atomicAdd(&my[e], 1);
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) {
-    int run = 0;
-    for (int w = 0; w < nwarps; ++w) {
-      const int c = cnt[w * E + e];
-      cnt[w * E + e] = run;
-      run += c;
+  // exclusive prefix over the warps, one expert per warp pass: lane l holds warp l's count
+  for (int e = warp; e < E; e += nwarps) {
+    const int c = (lane < nwarps) ? cnt[lane * ES + e] : 0;
+    int incl = c;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
     }
-    __stcg(p.hist + static_cast<int64_t>(blockIdx.x) * E + e, run);
+    if (lane < nwarps) cnt[lane * ES + e] = incl - c;
+    if (lane == 31) __stcg(p.hist + static_cast<int64_t>(blockIdx.x) * E + e, incl);
   }
   if (!grid_barrier(p.barrier, B)) return;
 
-  // totals and the counts of lower-numbered blocks: thread (g, e) sums the blocks b = g, g+G, ...
+  // totals and the counts of lower-numbered blocks: thread (g, e) sums the blocks g, g+G, ...
+  // Every block starts its walk at a different histogram row so that the SMs do not all ask
+  // the L2 for the same line at the same time.
   {
     const int G = max(1, static_cast<int>(blockDim.x) / E);
-    const int g = threadIdx.x / E, e = threadIdx.x % E;
+    const int g = threadIdx.x / E, e = threadIdx.x - g * E;
+    const int me = static_cast<int>(blockIdx.x);
     if (g < G) {
       for (int ee = e; ee < E; ee += blockDim.x) {  // one trip unless E > blockDim
         int t = 0, bfr = 0;
-        for (int b = g; b < B; b += G) {
+        const int trips = (B - g + G - 1) / G;      // blocks g, g+G, ... handled by this thread
+        int j = (me * 7) % (trips > 0 ? trips : 1);
+#pragma unroll 4
+        for (int it = 0; it < trips; ++it) {
+          const int b = g + j * G;
           const int v = __ldcg(p.hist + static_cast<int64_t>(b) * E + ee);
           t += v;
-          if (b < static_cast<int>(blockIdx.x)) bfr += v;
+          if (b < me) bfr += v;
+          if (++j == trips) j = 0;
         }
         atomicAdd(&total[ee], t);
         atomicAdd(&before[ee], bfr);
@@ -350,12 +334,15 @@ __global__ void __launch_bounds__(1024) route_align_coop_kernel(const CoopParams
     }
   }
   __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) padded[e] = (total[e] + p.bs - 1) / p.bs * p.bs;
+  __syncthreads();
   if (warp == 0) {
     const int chunk = (E + 31) / 32;
     const int e0 = lane * chunk;
     int sum = 0;
-    for (int e = e0; e < e0 + chunk && e < E; ++e) sum += (total[e] + p.bs - 1) / p.bs * p.bs;
+    for (int e = e0; e < e0 + chunk && e < E; ++e) sum += padded[e];
     int incl = sum;
+#pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
       const int o = __shfl_up_sync(0xffffffffu, incl, off);
       if (lane >= off) incl += o;
@@ -363,24 +350,19 @@ __global__ void __launch_bounds__(1024) route_align_coop_kernel(const CoopParams
     int run = incl - sum;
     for (int e = e0; e < e0 + chunk && e < E; ++e) {
       start[e] = run;
-      run += (total[e] + p.bs - 1) / p.bs * p.bs;
+      before[e] += run;   // write base of this block for expert e = padded start + lower blocks
+      run += padded[e];
     }
     if (lane == 31) start[E] = incl;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) {
-    const int e = i % E;
-    cnt[i] += start[e] + before[e];
-  }
-  __syncthreads();
-
-  // pass 2: stable scatter
+  // pass 2: stable scatter; position = block base + prefix over lower warps + rank in the row
   for (int b0 = wlo; b0 < whi; b0 += 32) {
     const int i = b0 + lane;
     const int e = (i < whi) ? sids[i] : -1;
     const unsigned grp = same_expert_lanes(e, p.nbits);
     int pos = 0;
-    if (e >= 0) pos = my[e] + __popc(grp & ((1u << lane) - 1u));
+    if (e >= 0) pos = before[e] + my[e] + __popc(grp & ((1u << lane) - 1u));
     __syncwarp();
     if (e >= 0) {
       if (lane == (__ffs(grp) - 1)) my[e] += __popc(grp);
@@ -390,7 +372,6 @@ __global__ void __launch_bounds__(1024) route_align_coop_kernel(const CoopParams
     }
     __syncwarp();
   }
-
   // padding entries, block -> expert table, tails: spread over the grid
   const int num_post = start[E];
   const int gwarp = blockIdx.x * nwarps + warp;
@@ -419,24 +400,19 @@ size_t coop_workspace_bytes(int E) {
 }
 
 // Returns FR_ERR_UNSUPPORTED when the case does not fit this kernel; the caller then uses the
-// cluster kernel.  logits == nullptr: align only (ids_in given).
-int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t stride_m, int64_t stride_e,
-                              int topk, float* weights, int32_t* ids_out, const int32_t* ids_in, int64_t n, int E,
-                              int bs, int32_t* sorted_ids, int64_t sorted_len, int32_t* expert_ids,
-                              int64_t expert_ids_len, int32_t* num_post, int32_t* counts, int32_t* inv_pos,
-                              void* workspace, size_t workspace_bytes, cudaStream_t st) {
+// cluster kernel.
+int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
+                        int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
+                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!workspace || workspace_bytes < coop_workspace_bytes(E) || (reinterpret_cast<uintptr_t>(workspace) & 15))
     return FR_ERR_UNSUPPORTED;
   if (n < kCoopMinAssignments || E > 1024) return FR_ERR_UNSUPPORTED;
-  if (logits && (topk > PK || E > 256 || (dtype != FR_F16 && dtype != FR_BF16))) return FR_ERR_UNSUPPORTED;
   const DeviceInfo& di = device_info();
   int grid = di.sm_count < 256 ? di.sm_count : 256;
   if (grid <= 0) return FR_ERR_UNSUPPORTED;
-  const int64_t unit = logits ? topk : 1;  // blocks own whole rows when routing
   int64_t per_block = (n + grid - 1) / grid;
-  per_block = (per_block + unit - 1) / unit * unit;
-  if (per_block < 1024) {                   // do not spread thinner than one assignment per thread
-    per_block = (1024 + unit - 1) / unit * unit;
+  if (per_block < 1024) {  // do not spread thinner than one assignment per thread
+    per_block = 1024;
     grid = static_cast<int>((n + per_block - 1) / per_block);
   }
   if (per_block > kCoopMaxPerBlock) return FR_ERR_UNSUPPORTED;
@@ -445,13 +421,6 @@ int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t 
   seg = (seg + 31) / 32 * 32;
 
   CoopParams p = {};
-  p.logits = logits;
-  p.M = M;
-  p.stride_m = stride_m;
-  p.stride_e = stride_e;
-  p.topk = topk;
-  p.weights = weights;
-  p.ids_out = ids_out;
   p.ids_in = ids_in;
   p.n = n;
   p.E = E;
@@ -467,34 +436,13 @@ int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t 
   p.barrier = static_cast<unsigned int*>(workspace);
   p.hist = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + 256);
   p.per_block = per_block;
-  p.rows_per_block = per_block / unit;
   p.seg = seg;
 
-  const size_t smem = (static_cast<size_t>(nwarps) * E + 3 * static_cast<size_t>(E) + 1 + per_block) * sizeof(int);
+  const size_t smem = (static_cast<size_t>(nwarps) * (E | 1) + 4 * static_cast<size_t>(E) + 1 + per_block) * sizeof(int);
   if (smem > 200 * 1024) return FR_ERR_UNSUPPORTED;
-
-  void (*kern)(CoopParams) = nullptr;
-  if (!logits) {
-    kern = route_align_coop_kernel<__half, 1>;
-  } else {
-    int L = 1;
-    while (L * 8 < E) L <<= 1;
-    p.vec_ok = (stride_e == 1) && (E == L * 8) && ((stride_m * 2) % 16 == 0) &&
-               ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
-#define FR_PICK(L_)                                                                       \
-  kern = (dtype == FR_F16) ? route_align_coop_kernel<__half, L_> : route_align_coop_kernel<__nv_bfloat16, L_>
-    switch (L) {
-      case 1: FR_PICK(1); break;
-      case 2: FR_PICK(2); break;
-      case 4: FR_PICK(4); break;
-      case 8: FR_PICK(8); break;
-      case 16: FR_PICK(16); break;
-      default: FR_PICK(32); break;
-    }
-#undef FR_PICK
-  }
   if (smem > 48 * 1024)
-    FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    FR_CUDA_OK(cudaFuncSetAttribute(align_coop_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(smem)));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(grid);
   cfg.blockDim = dim3(threads);
@@ -505,7 +453,7 @@ int route_align_coop_dispatch(const void* logits, int dtype, int64_t M, int64_t 
   attr[0].val.cooperative = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  FR_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, p));
+  FR_CUDA_OK(cudaLaunchKernelEx(&cfg, align_coop_kernel, p));
   return FR_OK;
 }
 

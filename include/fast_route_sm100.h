@@ -77,9 +77,8 @@ int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t*
              int32_t* counts, int32_t* inv_pos, void* workspace, size_t workspace_bytes, void* stream);
 
 /* fr_topk_softmax followed by fr_align on its compact [M,topk] ids: the routing/align
- * latency path (logits -> the five routing outputs).  With 16-bit logits, topk <= 8, E <= 256,
- * >= 8192 assignments and a workspace (same contract as fr_align) both stages run inside ONE
- * cooperative kernel; otherwise as two launches.  Outputs are identical either way. */
+ * latency path (logits -> the five routing outputs), two launches on the stream.  The
+ * workspace follows the contract of fr_align. */
 int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e,
                    int topk, float* weights, int32_t* ids, int block_size, int32_t* sorted_ids,
                    int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len,
