@@ -298,8 +298,18 @@ struct ExpertWs {
   int64_t rows, sorted_len, expert_ids_len;
   SplitPlan sp;
 };
+// The align stage's scratch (grid-barrier words + histogram) must sit at a fixed place of the
+// caller's workspace whatever the batch size, because it relies on being zero between calls:
+// it is always carved first, at offset 0.
+static void carve_align_ws(Carver& c, int E, void** ws, size_t* bytes) {
+  *bytes = coop_workspace_bytes(E);
+  *ws = c.take<uint8_t>(*bytes);
+}
+
 static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
   ExpertWs w;
+  w.align_ws = nullptr;
+  w.align_ws_bytes = 0;
   w.rows = rows_cap(n, E);
   w.sorted_len = round_up(n + static_cast<int64_t>(E) * (kBlockM - 1), kBlockM);
   w.expert_ids_len = w.sorted_len / kBlockM + 1;
@@ -307,8 +317,6 @@ static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
   w.expert_ids = c.take<int32_t>(w.expert_ids_len);
   w.num_post = c.take<int32_t>(4);
   w.inv_pos = c.take<int32_t>(n);
-  w.align_ws_bytes = coop_workspace_bytes(E);
-  w.align_ws = c.take<uint8_t>(w.align_ws_bytes);
   w.a_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
   w.act = c.take<uint16_t>(static_cast<size_t>(w.rows) * I);
   w.y_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
@@ -506,6 +514,9 @@ int fr_combine(const void* y, int64_t ld_y, int dtype, const int32_t* inv_pos, i
 size_t fr_moe_workspace_bytes(int64_t M, int H, int I, int E, int topk) {
   if (M <= 0 || H <= 0 || I <= 0 || E <= 0 || topk <= 0) return 0;
   Carver c(nullptr);
+  void* aws;
+  size_t aws_bytes;
+  carve_align_ws(c, E, &aws, &aws_bytes);
   carve_route(c, M, H, E, topk);
   c.take<float>(M * topk);
   c.take<int32_t>(M * topk);
@@ -526,10 +537,15 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
   if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   Carver c(workspace);
+  void* aws;
+  size_t aws_bytes;
+  carve_align_ws(c, E, &aws, &aws_bytes);
   RouteWs rws = carve_route(c, M, H, E, topk);
   float* tw = c.take<float>(M * topk);
   int32_t* ti = c.take<int32_t>(M * topk);
   ExpertWs ews = carve_experts(c, M * topk, H, I, E);
+  ews.align_ws = aws;
+  ews.align_ws_bytes = aws_bytes;
   if (topk_weights_out) tw = topk_weights_out;
   if (topk_ids_out) ti = topk_ids_out;
   int rc = route_fused_impl(x, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
@@ -541,6 +557,9 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
 size_t fr_moe_experts_workspace_bytes(int64_t R, int H, int I, int E_local) {
   if (R <= 0 || H <= 0 || I <= 0 || E_local <= 0) return 0;
   Carver c(nullptr);
+  void* aws;
+  size_t aws_bytes;
+  carve_align_ws(c, E_local, &aws, &aws_bytes);
   carve_experts(c, R, H, I, E_local);
   return c.total();
 }
@@ -555,7 +574,12 @@ int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row
   if (!workspace || workspace_bytes < fr_moe_experts_workspace_bytes(R, H, I, E_local)) return FR_ERR_WORKSPACE;
   if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
   Carver c(workspace);
+  void* aws;
+  size_t aws_bytes;
+  carve_align_ws(c, E_local, &aws, &aws_bytes);
   ExpertWs ews = carve_experts(c, R, H, I, E_local);
+  ews.align_ws = aws;
+  ews.align_ws_bytes = aws_bytes;
   return experts_impl(rows, H, row_expert, row_weight, w1, w2, dtype, R, 1, H, I, E_local, y, H, ews,
                       static_cast<cudaStream_t>(stream));
 }

@@ -50,9 +50,15 @@ def _rank_main(rank, world, port, M, H, I, E, k, skew, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("M,H,I,E,k,skew", [(512, 512, 768, 8, 2, False), (300, 256, 384, 16, 4, True),
-                                             (3, 512, 1024, 8, 2, False)])
-def test_ep_layer_matches_single_gpu(M, H, I, E, k, skew):
+@pytest.mark.parametrize("M,H,I,E,k,skew,exact", [(512, 512, 768, 8, 2, False, False),
+                                                   (300, 256, 384, 16, 4, True, False),
+                                                   (3, 512, 1024, 8, 2, False, False),
+                                                   (4096, 2048, 1024, 8, 2, False, True)])
+def test_ep_layer_matches_single_gpu(M, H, I, E, k, skew, exact):
+    """`exact` cases are large enough that neither run uses split-K: the same kernels see the same
+    rows and the outputs are bit-identical.  The small cases slice K differently on a GPU holding all
+    rows than on GPUs holding a share (different fp32 summation order, and the split-K path skips the
+    per-slot bf16 rounding), so they are held to the layer tolerance instead."""
     world = min(torch.cuda.device_count(), 4)
     if world < 2:
         pytest.skip("needs at least 2 GPUs")
@@ -69,6 +75,5 @@ def test_ep_layer_matches_single_gpu(M, H, I, E, k, skew):
         p.join(timeout=60)
         assert p.exitcode == 0
     for rank, err, same, refmax in res:
-        # same kernels on the same rows; only the split-K slicing of tiny batches may differ
-        assert err <= 2e-2, (rank, err, refmax)
+        assert err == 0.0 if exact else err <= 2e-2 + refmax * 2.0 ** -7, (rank, err, refmax)
         assert same
