@@ -30,6 +30,7 @@ SIGNATURES = {
     "fr_topk_softmax": (_I, [_P, _I, _L, _I, _L, _L, _I, _I, _P, _L, _P, _L, _I, _P]),
     "fr_align_workspace_bytes": (_Z, [_I]),
     "fr_align": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _P, _P, _Z, _P]),
+    "fr_align_noalloc": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _P, _P]),
     "fr_route_align": (_I, [_P, _I, _L, _I, _L, _L, _I, _P, _P, _I, _P, _L, _P, _L, _P, _P, _Z, _P]),
     "fr_route_fused_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fr_route_fused": (_I, [_P, _I, _L, _I, _L, _P, _L, _L, _I, _I, _I, _P, _P, _P, _P, _Z, _P]),

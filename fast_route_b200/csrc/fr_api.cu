@@ -12,6 +12,9 @@ int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* s
                    int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
                    int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st);
 size_t coop_workspace_bytes(int E);
+int align_noalloc_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids,
+                           int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post,
+                           int32_t* counts, int32_t* inv_pos, cudaStream_t st);
 int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, int dtype, int64_t max_rows,
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
@@ -403,6 +406,13 @@ int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t*
   return align_dispatch(topk_ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
                         num_tokens_post_pad, counts, inv_pos, workspace, workspace_bytes,
                         static_cast<cudaStream_t>(stream));
+}
+
+int fr_align_noalloc(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids,
+                     int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad,
+                     int32_t* counts, int32_t* inv_pos, void* stream) {
+  return align_noalloc_dispatch(topk_ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
+                                num_tokens_post_pad, counts, inv_pos, static_cast<cudaStream_t>(stream));
 }
 
 int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e, int topk,

@@ -27,7 +27,8 @@ int launch_topk16(const void* logits, int64_t M, int E, int64_t stride_m, int64_
                   int64_t w_stride, int32_t* ids, int64_t id_stride, cudaStream_t st);
 int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                         int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st);
+                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st,
+                        int64_t min_n = 8192);
 
 __device__ __forceinline__ bool beats(float v, int c, float bv, int bc) {
   return (v > bv) || (v == bv && c < bc);

@@ -392,7 +392,6 @@ __global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
 }
 
 constexpr int kCoopMaxPerBlock = 8192;
-constexpr int64_t kCoopMinAssignments = 8192;
 
 size_t coop_workspace_bytes(int E) {
   // histogram for up to 256 blocks + the two barrier words (kept 256 bytes apart from the histogram)
@@ -403,10 +402,10 @@ size_t coop_workspace_bytes(int E) {
 // cluster kernel.
 int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                         int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st, int64_t min_n) {
   if (!workspace || workspace_bytes < coop_workspace_bytes(E) || (reinterpret_cast<uintptr_t>(workspace) & 15))
     return FR_ERR_UNSUPPORTED;
-  if (n < kCoopMinAssignments || E > 1024) return FR_ERR_UNSUPPORTED;
+  if (n < min_n || n < 1 || E > 1024) return FR_ERR_UNSUPPORTED;
   const DeviceInfo& di = device_info();
   int grid = di.sm_count < 256 ? di.sm_count : 256;
   if (grid <= 0) return FR_ERR_UNSUPPORTED;
@@ -455,6 +454,55 @@ int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t
   cfg.numAttrs = 1;
   FR_CUDA_OK(cudaLaunchKernelEx(&cfg, align_coop_kernel, p));
   return FR_OK;
+}
+
+// ----------------------------------------------------------------------------------
+// fr_align_noalloc: the cooperative align kernel with its scratch in library-owned device
+// memory instead of a caller workspace.
+// ----------------------------------------------------------------------------------
+constexpr int kNoAllocMaxExperts = FR_ALIGN_NOALLOC_MAX_EXPERTS;
+constexpr size_t kNoAllocScratchBytes = 256 + static_cast<size_t>(256) * kNoAllocMaxExperts * sizeof(int32_t);
+
+// Barrier words + per-block histograms for up to kNoAllocMaxExperts experts.  Every GPU that
+// loads the library holds these 257 KB until the process exits.
+static __device__ __align__(256) unsigned char g_align_noalloc_scratch[kNoAllocScratchBytes];
+
+// In host code the array's name is only a handle; the device address comes from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+static int noalloc_scratch_ptr(void** out) {
+  constexpr int kMaxDevices = 64;
+  static void* cached[kMaxDevices] = {};
+  int dev = 0;
+  FR_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return FR_ERR_UNSUPPORTED;
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    FR_CUDA_OK(cudaGetSymbolAddress(&ptr, g_align_noalloc_scratch));
+    if (!ptr) return FR_ERR_DRIVER;
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return FR_OK;
+}
+
+int align_noalloc_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids,
+                           int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post,
+                           int32_t* counts, int32_t* inv_pos, cudaStream_t st) {
+  if (!topk_ids || !sorted_ids || !expert_ids || !num_post || n < 1 || E <= 0 || bs <= 0) return FR_ERR_ARG;
+  if (E > kNoAllocMaxExperts) return FR_ERR_UNSUPPORTED;                      // beyond the built-in scratch
+  const DeviceInfo& di = device_info();
+  if (n > static_cast<int64_t>(di.sm_count < 256 ? di.sm_count : 256) * kCoopMaxPerBlock) return FR_ERR_UNSUPPORTED;
+  if (sorted_len < n + static_cast<int64_t>(E) * (bs - 1)) return FR_ERR_ARG;
+  if (expert_ids_len < (n + static_cast<int64_t>(E) * (bs - 1)) / bs) return FR_ERR_ARG;
+  void* scratch = nullptr;
+  const int rc = noalloc_scratch_ptr(&scratch);
+  if (rc) return rc;
+  // The array keeps whatever the previous call left.  Only the two barrier words must start
+  // at zero (a call that ended in a reported timeout could have left a count behind); the
+  // histogram rows are fully rewritten before they are read.
+  FR_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
+  return align_coop_dispatch(topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post,
+                             counts, inv_pos, scratch, kNoAllocScratchBytes, st, /*min_n=*/1);
 }
 
 }  // namespace fr

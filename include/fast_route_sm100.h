@@ -76,6 +76,25 @@ int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t*
              int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad,
              int32_t* counts, int32_t* inv_pos, void* workspace, size_t workspace_bytes, void* stream);
 
+/* fr_align for callers that cannot hand over scratch memory of their own: code that runs where
+ * cudaMalloc is off limits (inside a caller-managed memory pool or arena with nothing left to
+ * carve, from a plugin whose host forbids device allocation after start-up, or on a hot path
+ * that must never reach the allocator).  It has no counterpart in the reference.  It runs the
+ * same whole-GPU cooperative kernel as fr_align, with the histogram and barrier words kept in a
+ * 257 KB array that the library itself owns on every GPU that loads it, until the process
+ * exits.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Limits: E <= FR_ALIGN_NOALLOC_MAX_EXPERTS and 1 <= n <= 8192 * (number of SMs); anything
+ * larger returns FR_ERR_UNSUPPORTED (use fr_align with a workspace).  Outputs are identical
+ * to fr_align's.
+ * The first call on each device looks up the array's device address (make that call with the
+ * device current, before any stream capture starts).  All calls on a device share the one
+ * array: calls whose kernels could overlap on the GPU (different streams) race on it and must
+ * be serialised by the caller.  The barrier words are cleared at the start of every call. */
+#define FR_ALIGN_NOALLOC_MAX_EXPERTS 256
+int fr_align_noalloc(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids,
+                     int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len,
+                     int32_t* num_tokens_post_pad, int32_t* counts, int32_t* inv_pos, void* stream);
+
 /* fr_topk_softmax followed by fr_align on its compact [M,topk] ids: the routing/align
  * latency path (logits -> the five routing outputs), two launches on the stream.  The
  * workspace follows the contract of fr_align. */
