@@ -487,7 +487,12 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
   p.kb_per_split = (KB + split_k - 1) / split_k;
   p.split_k = (KB + p.kb_per_split - 1) / p.kb_per_split;  // drop empty slices
   split_k = p.split_k;
-  p.group_m = 16;
+  // Row blocks per tile group (all column tiles of a group are walked before the next group).
+  // A group's A rows stay in L2 while its B tiles stream through; with ~32 row blocks per
+  // expert a group of 32 lets each expert's weights be fetched from HBM once instead of twice,
+  // with few blocks per expert a wider group only spreads the in-flight tiles over more experts.
+  const int64_t blocks_per_expert = n_valid / (static_cast<int64_t>(BM) * E);
+  p.group_m = blocks_per_expert >= 24 ? (which == 0 ? 32 : 24) : 16;
   p.partial_cols = static_cast<int64_t>(p.num_nb) * GEMM_BN;
   if (split_k > 1) {
     const size_t need = static_cast<size_t>(split_k) * static_cast<size_t>(n_valid) * p.partial_cols * sizeof(float);
