@@ -33,6 +33,9 @@ WORKLOADS = {
     "mixtral-8x7b": (4096, 14336, 8, 2),
     "mixtral-8x22b": (6144, 16384, 8, 2),
     "fine-grained-64e": (2048, 1408, 64, 6),
+    # same layer with a Zipf(1.2) preference over experts: the last input feature is the constant 1
+    # and carries a per-expert bias in the gate, so the hottest expert gets ~15x the mean load
+    "fine-grained-64e-zipf": (2048, 1408, 64, 6),
 }
 
 
@@ -339,6 +342,10 @@ def run_ours(args, rank, world, local_rank):
 
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     xs = [torch.randn(M, H, device=dev, dtype=dtype, generator=g) for _ in range(3)]
+    if args.workload.endswith("-zipf"):
+        wg[:, H - 1] = synth.zipf_gate_bias(E, 1.2, 1.6).to(device=dev, dtype=dtype)
+        for xb in xs:
+            xb[:, H - 1] = 1.0
 
     def barrier():
         if world > 1:
@@ -369,6 +376,12 @@ def run_ours(args, rank, world, local_rank):
     total_tokens = M * world
     value = total_tokens / ms_per_step * 1e3
     _lib.raise_on_device_error()
+    if world == 1:
+        _, _, ti0 = fr.fused_moe(xs[0], wg.t(), w1, w2, k, return_routing=True)
+        load = torch.bincount(ti0.flatten().long(), minlength=E).float()
+        expert_load = {"max_over_mean": float(load.max() / load.mean()), "experts_without_tokens": int((load == 0).sum())}
+    else:
+        expert_load = None
 
     if args.profile:
         if rank == 0:
@@ -418,7 +431,7 @@ def run_ours(args, rank, world, local_rank):
         "tflops": flops / ms_per_step / 1e9,
         "frac_tensor_peak": flops / ms_per_step / 1e9 / (peaks["bf16_tflops_sustained"] * world),
         "frac_tensor_peak_note": f"of {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_tflops_sustained']} TF/GPU)",
-        "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "expert_load": expert_load,
     }
     if world == 1:
         line["roofline"] = gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps=max(5, args.steps))
@@ -428,7 +441,7 @@ def run_ours(args, rank, world, local_rank):
             line["roofline"]["traffic"] = 4.15e9
             line["roofline"]["traffic_note"] = ("DRAM bytes per GEMM1 launch (ncu, one pass); algorithmic bytes are "
                                                 "2.16 GB read (weights + A once) + 0.97 GB written")
-        if not args.no_sweep:
+        if not args.no_sweep and args.workload == "mixtral-8x7b":
             Ms = [m for m in (1, 4, 16, 64, 256, 1024, 4096, 16384)]
             line["sweep"] = sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms)
             line["routing_latency"] = routing_latency(fr, synth, dev)
