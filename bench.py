@@ -331,8 +331,9 @@ def run_ours(args, rank, world, local_rank):
         dist.broadcast(wg, src=0)
 
         def layer(xb):
-            return ep.fused_moe_ep(xb, wg.t(), w1, w2, k, group)
-        launches_per_step = 12
+            return ep.fused_moe_ep(xb, wg.t(), w1, w2, k, group, chunks=args.ep_chunks)
+        ch = args.ep_chunks or 1
+        launches_per_step = 12 * ch
     else:
         wg, w1, w2 = make_weights(H, I, E, dev, seed=0)
 
@@ -463,6 +464,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens in the CPU baseline's sample")
     ap.add_argument("--cpu-budget", type=float, default=120.0,
                     help="seconds the reference arm may spend in its timed passes (the sample shrinks to fit)")
+    ap.add_argument("--ep-chunks", type=int, default=None,
+                    help="token chunks pipelined through dispatch/experts/return with N > 1 (default 1)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--routing-only", action="store_true",

@@ -43,6 +43,9 @@ SIGNATURES = {
     "fr_moe_layer": (_I, [_P, _P, _L, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "fr_moe_experts_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fr_moe_experts": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _P, _Z, _P]),
+    "fr_moe_experts_rows_cap": (_L, [_L, _I]),
+    "fr_moe_experts_peer": (_I, [_P, _L, _I, _L, _P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _L, _P, _P, _Z, _P]),
+    "fr_combine_peer": (_I, [_P, _L, _I, _L, _I, _P, _P, _L, _I, _I, _P, _L, _P]),
     "fr_gather_rows": (_I, [_P, _L, _P, _L, _I, _P, _L, _P]),
 }
 

@@ -103,6 +103,68 @@ __global__ void transpose_gate_kernel(const uint16_t* __restrict__ gate, int64_t
   out[i] = h < H ? gate[h * sh + e * se] : static_cast<uint16_t>(0);
 }
 
+// Expert-parallel dispatch fused into the gather: row p of the expert-sorted A operand is read
+// straight from the memory of the GPU that owns the token (peer pointers over NVLink, plain
+// 16-byte loads; the local GPU is just one more entry of the table).
+//   a_sorted[p,:] = peer_base[src_rank[r]][src_row[r], :],  r = sorted_ids[p]
+__global__ void __launch_bounds__(256) permute_rows_peer_kernel(const uint4* const* __restrict__ peer_base,
+                                                                int64_t ld_src_v, int world, int64_t peer_rows,
+                                                                const int32_t* __restrict__ src_rank,
+                                                                const int32_t* __restrict__ src_row,
+                                                                const int32_t* __restrict__ sorted_ids,
+                                                                const int32_t* __restrict__ num_post, int64_t n,
+                                                                uint4* __restrict__ dst, int64_t ld_dst_v, int row_v) {
+  const int64_t row = blockIdx.x;
+  if (row >= __ldg(num_post)) return;
+  const int32_t sid = __ldg(sorted_ids + row);
+  uint4* d = dst + row * ld_dst_v;
+  bool ok = sid >= 0 && sid < n;
+  int r = 0, t = 0;
+  if (ok) {
+    r = __ldg(src_rank + sid);
+    t = __ldg(src_row + sid);
+    ok = r >= 0 && r < world && t >= 0 && t < peer_rows;
+    if (!ok && threadIdx.x == 0) report(ST_BAD_SORTED_ID, static_cast<unsigned int>(sid));
+  }
+  if (ok) {
+    const uint4* s = peer_base[r] + static_cast<int64_t>(t) * ld_src_v;
+    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = s[v];
+  } else {
+    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = make_uint4(0, 0, 0, 0);
+  }
+}
+
+// Expert-parallel return fused into the combine: the k result rows of a token are read from the
+// GPUs that computed them.  out[t,:] = sum_j peer_y[rank_of[t*k+j]][pos_of[t*k+j], :]
+template <bool BF16>
+__global__ void __launch_bounds__(256) combine_peer_kernel(const uint4* const* __restrict__ peer_y, int64_t ld_y_v,
+                                                           int world, int64_t peer_rows,
+                                                           const int32_t* __restrict__ rank_of,
+                                                           const int32_t* __restrict__ pos_of, int topk, int row_v,
+                                                           uint4* __restrict__ out, int64_t ld_out_v) {
+  const int64_t t = blockIdx.x;
+  for (int v = threadIdx.x; v < row_v; v += blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    for (int j = 0; j < topk; ++j) {
+      const int r = __ldg(rank_of + t * topk + j);
+      const int pos = __ldg(pos_of + t * topk + j);
+      if (r < 0 || r >= world || pos < 0 || pos >= peer_rows) continue;
+      const uint4 raw = peer_y[r][static_cast<int64_t>(pos) * ld_y_v + v];
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<BF16>(w[i]);
+        acc[2 * i] += f.x;
+        acc[2 * i + 1] += f.y;
+      }
+    }
+    out[t * ld_out_v + v] = make_uint4(pack2<BF16>(acc[0], acc[1]), pack2<BF16>(acc[2], acc[3]),
+                                       pack2<BF16>(acc[4], acc[5]), pack2<BF16>(acc[6], acc[7]));
+  }
+}
+
 // Router for a handful of rows (decode-sized batches): one CTA per token, the H-long dot
 // products are split over the threads (fp32 FMA, fixed reduction order), then warp 0 ranks
 // the E logits by counting (ties -> lower expert id) and writes the top-k and its softmax.
@@ -362,6 +424,29 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
   return static_cast<int>(cudaGetLastError());
 }
 
+// Expert side of the peer-memory path: align the received rows by local expert, gather them from
+// their owners, run both GEMMs; results stay in expert-sorted order in y_sorted (memory the other
+// ranks can read) and inv_pos_out tells where each received row ended up.
+static int experts_peer_impl(const void* const* peer_x, int64_t ld_x, int world, int64_t peer_rows,
+                             const int32_t* src_rank, const int32_t* src_row, const int32_t* row_expert,
+                             const float* row_weight, const void* w1, const void* w2, int dtype, int64_t R, int H,
+                             int I, int E, void* y_sorted, int64_t y_rows, int32_t* inv_pos_out, const ExpertWs& w,
+                             cudaStream_t st) {
+  if (y_rows < w.rows) return FR_ERR_WORKSPACE;
+  int rc = align_dispatch(row_expert, R, E, kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
+                          w.num_post, nullptr, inv_pos_out, w.align_ws, w.align_ws_bytes, st);
+  if (rc) return rc;
+  permute_rows_peer_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
+      reinterpret_cast<const uint4* const*>(peer_x), ld_x / 8, world, peer_rows, src_rank, src_row, w.sorted,
+      w.num_post, R, reinterpret_cast<uint4*>(w.a_sorted), H / 8, H / 8);
+  FR_CUDA_OK(cudaGetLastError());
+  rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
+                             w.sorted, nullptr, R, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
+  if (rc) return rc;
+  return gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
+                               row_weight, R, y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, nullptr);
+}
+
 }  // namespace fr
 
 using namespace fr;
@@ -463,6 +548,52 @@ int fr_permute_rows(const void* src, int dtype, int H, int64_t ld_src, const int
   permute_rows_kernel<<<static_cast<unsigned>(max_rows), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), ld_src / 8, sorted_ids, num_tokens_post_pad, n, topk,
       static_cast<uint4*>(dst), ld_dst / 8, H / 8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+int64_t fr_moe_experts_rows_cap(int64_t R, int E_local) { return R > 0 && E_local > 0 ? rows_cap(R, E_local) : 0; }
+
+int fr_moe_experts_peer(const void* const* peer_x, int64_t ld_x, int world, int64_t peer_rows,
+                        const int32_t* src_rank, const int32_t* src_row, const int32_t* row_expert,
+                        const float* row_weight, const void* w1, const void* w2, int dtype, int64_t R, int H, int I,
+                        int E_local, void* y_sorted, int64_t y_rows, int32_t* inv_pos_out, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+  if (!peer_x || !src_rank || !src_row || !row_expert || !w1 || !w2 || !y_sorted || !inv_pos_out || R < 0 ||
+      H <= 0 || I <= 0 || E_local <= 0 || world <= 0 || peer_rows <= 0)
+    return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (I % 8) || (ld_x % 8)) return FR_ERR_ALIGN;
+  if (R == 0) return FR_OK;
+  if (!workspace || workspace_bytes < fr_moe_experts_workspace_bytes(R, H, I, E_local)) return FR_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 1023) || (reinterpret_cast<uintptr_t>(y_sorted) & 15))
+    return FR_ERR_ALIGN;
+  Carver c(workspace);
+  void* aws;
+  size_t aws_bytes;
+  carve_align_ws(c, E_local, &aws, &aws_bytes);
+  ExpertWs ews = carve_experts(c, R, H, I, E_local);
+  ews.align_ws = aws;
+  ews.align_ws_bytes = aws_bytes;
+  return experts_peer_impl(peer_x, ld_x, world, peer_rows, src_rank, src_row, row_expert, row_weight, w1, w2, dtype,
+                           R, H, I, E_local, y_sorted, y_rows, inv_pos_out, ews, static_cast<cudaStream_t>(stream));
+}
+
+int fr_combine_peer(const void* const* peer_y, int64_t ld_y, int world, int64_t peer_rows, int dtype,
+                    const int32_t* rank_of, const int32_t* pos_of, int64_t M, int topk, int H, void* out,
+                    int64_t ld_out, void* stream) {
+  if (!peer_y || !rank_of || !pos_of || !out || M < 0 || topk <= 0 || H <= 0 || world <= 0) return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (ld_y % 8) || (ld_out % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return FR_ERR_ALIGN;
+  if (M == 0) return FR_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FR_BF16)
+    combine_peer_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
+        reinterpret_cast<const uint4* const*>(peer_y), ld_y / 8, world, peer_rows, rank_of, pos_of, topk, H / 8,
+        static_cast<uint4*>(out), ld_out / 8);
+  else
+    combine_peer_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(
+        reinterpret_cast<const uint4* const*>(peer_y), ld_y / 8, world, peer_rows, rank_of, pos_of, topk, H / 8,
+        static_cast<uint4*>(out), ld_out / 8);
   return static_cast<int>(cudaGetLastError());
 }
 

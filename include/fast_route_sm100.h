@@ -179,6 +179,29 @@ int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row
                    const void* w2, int dtype, int64_t R, int H, int I, int E_local, void* y, void* workspace,
                    size_t workspace_bytes, void* stream);
 
+/* Expert parallelism over peer memory (NVLink loads, no send/receive buffers; no counterpart in
+ * the reference).  peer_x / peer_y are DEVICE arrays of `world` base pointers, one per rank, to
+ * buffers of identical shape [peer_rows, H] that every GPU of the node can read (symmetric
+ * memory); entry `rank` of the table may be the local buffer.
+ * fr_moe_experts_peer: the R rows this rank's experts must process are described by
+ * (src_rank[r], src_row[r]) = where the token lives, row_expert[r] in [0, E_local) and
+ * row_weight[r] (may be NULL).  The gather that builds the expert-sorted A operand reads them
+ * from their owners; both grouped GEMMs run; results stay in expert-sorted order in
+ * y_sorted[y_rows, H] (y_rows >= fr_moe_experts_rows_cap(R, E_local)); inv_pos_out[r] is the
+ * row of y_sorted holding the result of received row r.  Workspace as fr_moe_experts.
+ * fr_combine_peer: out[t,:] = sum_j peer_y[rank_of[t*topk+j]][pos_of[t*topk+j], :] in fp32, slot
+ * order.  The caller orders the ranks (a small collective before and after): peers' x must be
+ * complete before the gather, peers' y_sorted before the combine. */
+int64_t fr_moe_experts_rows_cap(int64_t R, int E_local);
+int fr_moe_experts_peer(const void* const* peer_x, int64_t ld_x, int world, int64_t peer_rows,
+                        const int32_t* src_rank, const int32_t* src_row, const int32_t* row_expert,
+                        const float* row_weight, const void* w1, const void* w2, int dtype, int64_t R, int H,
+                        int I, int E_local, void* y_sorted, int64_t y_rows, int32_t* inv_pos_out,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int fr_combine_peer(const void* const* peer_y, int64_t ld_y, int world, int64_t peer_rows, int dtype,
+                    const int32_t* rank_of, const int32_t* pos_of, int64_t M, int topk, int H, void* out,
+                    int64_t ld_out, void* stream);
+
 /* Gather rows by index: dst[i,:] = src[idx[i],:] (idx < 0 writes zeros); 16-byte vectors. */
 int fr_gather_rows(const void* src, int64_t ld_src, const int32_t* idx, int64_t rows, int row_bytes, void* dst,
                    int64_t ld_dst, void* stream);

@@ -20,7 +20,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, M, H, I, E, k, skew, q):
+def _rank_main(rank, world, port, M, H, I, E, k, skew, chunks, q, p2p=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import datetime
@@ -39,8 +39,13 @@ def _rank_main(rank, world, port, M, H, I, E, k, skew, q):
                                                gate_bias=bias)
         lo, hi = group.local_expert_range()
         x = x_all[rank * M:(rank + 1) * M].contiguous().to(dev)
-        out = ep.fused_moe_ep(x, gate.to(dev), w1[lo:hi].contiguous().to(dev), w2[lo:hi].contiguous().to(dev), k, group)
-        out2 = ep.fused_moe_ep(x, gate.to(dev), w1[lo:hi].contiguous().to(dev), w2[lo:hi].contiguous().to(dev), k, group)
+        args = (x, gate.to(dev), w1[lo:hi].contiguous().to(dev), w2[lo:hi].contiguous().to(dev), k, group)
+        if p2p:
+            out = ep.fused_moe_ep_p2p(*args)
+            out2 = ep.fused_moe_ep_p2p(*args)
+        else:
+            out = ep.fused_moe_ep(*args, chunks=chunks)
+            out2 = ep.fused_moe_ep(*args, chunks=chunks)
         ref = fr.fused_moe(x_all.to(dev), gate.to(dev), w1.to(dev), w2.to(dev), k)[rank * M:(rank + 1) * M]
         torch.cuda.synchronize()
         _lib.raise_on_device_error()
@@ -50,11 +55,26 @@ def _rank_main(rank, world, port, M, H, I, E, k, skew, q):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("M,H,I,E,k,skew,chunks,exact", [(512, 512, 768, 8, 2, False, 1, False),
+                                                          (300, 256, 384, 16, 4, True, 3, False),
+                                                          (3, 512, 1024, 8, 2, False, None, False),
+                                                          (4096, 2048, 1024, 8, 2, False, 1, True),
+                                                          (4096, 2048, 1024, 8, 2, False, 2, False)])
+def test_ep_layer_matches_single_gpu(M, H, I, E, k, skew, chunks, exact):
+    _run_ep(M, H, I, E, k, skew, chunks, exact, False)
+
+
 @pytest.mark.parametrize("M,H,I,E,k,skew,exact", [(512, 512, 768, 8, 2, False, False),
                                                    (300, 256, 384, 16, 4, True, False),
                                                    (3, 512, 1024, 8, 2, False, False),
                                                    (4096, 2048, 1024, 8, 2, False, True)])
-def test_ep_layer_matches_single_gpu(M, H, I, E, k, skew, exact):
+def test_ep_peer_memory_layer_matches_single_gpu(M, H, I, E, k, skew, exact):
+    """The peer-memory path (NVLink gather / combine, 8 + 4 bytes of metadata per assignment through
+    NCCL) against the single-GPU layer; NVLS is off in the child processes."""
+    _run_ep(M, H, I, E, k, skew, 1, exact, True)
+
+
+def _run_ep(M, H, I, E, k, skew, chunks, exact, p2p):
     """`exact` cases are large enough that neither run uses split-K: the same kernels see the same
     rows and the outputs are bit-identical.  The small cases slice K differently on a GPU holding all
     rows than on GPUs holding a share (different fp32 summation order, and the split-K path skips the
@@ -67,10 +87,23 @@ def test_ep_layer_matches_single_gpu(M, H, I, E, k, skew, exact):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, M, H, I, E, k, skew, q)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, M, H, I, E, k, skew, chunks, q, p2p)) for r in range(world)]
     for p in procs:
         p.start()
-    res = sorted(q.get(timeout=300) for _ in range(world))
+    import queue
+    import time
+    res, deadline = [], time.time() + 240
+    while len(res) < world:
+        try:
+            res.append(q.get(timeout=2))
+        except queue.Empty:
+            dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
+            if dead or time.time() > deadline:
+                for p in procs:
+                    if p.is_alive():
+                        p.kill()          # exact child processes started above
+                pytest.fail(f"a rank failed or timed out (exit codes {[p.exitcode for p in procs]})")
+    res.sort()
     for p in procs:
         p.join(timeout=60)
         assert p.exitcode == 0
