@@ -330,10 +330,20 @@ def run_ours(args, rank, world, local_rank):
         # the gate is replicated: same seed stream on every rank would differ after the experts, so broadcast it
         dist.broadcast(wg, src=0)
 
-        def layer(xb):
-            return ep.fused_moe_ep(xb, wg.t(), w1, w2, k, group, chunks=args.ep_chunks)
-        ch = args.ep_chunks or 1
-        launches_per_step = 12 * ch
+        if args.ep_mode == "p2p":
+            def layer(xb):
+                return ep.fused_moe_ep_p2p(xb, wg.t(), w1, w2, k, group)
+            launches_per_step = 9
+            try:        # symmetric memory needs peer access between all GPUs of the node
+                layer(torch.zeros(M, H, device=dev, dtype=dtype))
+            except Exception as err:        # every rank fails the same way at the collective set-up
+                if rank == 0:
+                    print(f"peer-memory path unavailable ({err}); using NCCL all-to-all", file=sys.stderr)
+                args.ep_mode = "nccl"
+        if args.ep_mode == "nccl":
+            def layer(xb):
+                return ep.fused_moe_ep(xb, wg.t(), w1, w2, k, group, chunks=args.ep_chunks)
+            launches_per_step = 12 * (args.ep_chunks or 1)
     else:
         wg, w1, w2 = make_weights(H, I, E, dev, seed=0)
 
@@ -426,7 +436,8 @@ def run_ours(args, rank, world, local_rank):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload} MoE layer H={H} I={I} E={E} top-{k}, M={M} tokens per GPU per step",
-                   "parallelism": "single GPU" if world == 1 else f"expert parallel ep{world} + token data parallel",
+                   "parallelism": "single GPU" if world == 1 else
+                   f"expert parallel ep{world} + token data parallel, rows moved by {args.ep_mode}",
                    "l2": "weights (2.8 GB) and activations far exceed the 126 MB L2; no explicit flush",
                    "tokens_per_step_total": total_tokens},
         "tflops": flops / ms_per_step / 1e9,
@@ -464,6 +475,9 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=1024, help="tokens in the CPU baseline's sample")
     ap.add_argument("--cpu-budget", type=float, default=120.0,
                     help="seconds the reference arm may spend in its timed passes (the sample shrinks to fit)")
+    ap.add_argument("--ep-mode", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: token rows move by peer-memory loads inside the gather / combine kernels (p2p) "
+                         "or through NCCL all-to-all send/receive buffers (nccl)")
     ap.add_argument("--ep-chunks", type=int, default=None,
                     help="token chunks pipelined through dispatch/experts/return with N > 1 (default 1)")
     ap.add_argument("--no-sweep", action="store_true")

@@ -71,12 +71,13 @@ def validate_counts(counts: torch.Tensor, n_assignments: int, recv_counts: torch
         raise RuntimeError("negative row count received from a peer")
 
 
-def recv_row_experts(recv_counts: torch.Tensor) -> torch.Tensor:
+def recv_row_experts(recv_counts: torch.Tensor, total: int = None) -> torch.Tensor:
     """Local expert id of every received row.  Rows arrive grouped by source rank and,
-    inside a source's segment, by expert in ascending order."""
+    inside a source's segment, by expert in ascending order.  ``total`` (the number of
+    received rows, known on the host from the split sizes) avoids a device synchronisation."""
     world, epr = recv_counts.shape
     pattern = torch.arange(epr, dtype=torch.int32, device=recv_counts.device).repeat(world)
-    return torch.repeat_interleave(pattern, recv_counts.reshape(-1).long())
+    return torch.repeat_interleave(pattern, recv_counts.reshape(-1).long(), output_size=total)
 
 
 def all_to_all_rows(send: torch.Tensor, in_splits: List[int], out_splits: List[int], group: ExpertParallelGroup,
@@ -161,7 +162,7 @@ def fused_moe_ep(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: torc
         R = c["recv_rows"].shape[0]
         y = torch.empty(R, H, dtype=hidden_states.dtype, device=dev)
         if R:
-            row_expert = recv_row_experts(c["recv_counts"])
+            row_expert = recv_row_experts(c["recv_counts"], R)
             nbytes = lib.fr_moe_experts_workspace_bytes(R, H, I, El)
             ws = _lib.workspace(nbytes, dev, "ep_experts")
             rc = lib.fr_moe_experts(_lib.ptr(c["recv_rows"]), _lib.ptr(row_expert), _lib.ptr(c["recv_w"]),
@@ -262,10 +263,10 @@ def fused_moe_ep_p2p(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: 
     inv_out = torch.empty(max(R, 1), dtype=torch.int32, device=dev)
     if R:
         src_rank = torch.repeat_interleave(torch.arange(W, dtype=torch.int32, device=dev),
-                                           torch.tensor(out_splits, device=dev))
+                                           recv_counts.sum(dim=1), output_size=R)
         src_row = recv_meta[:, 0].contiguous()
         row_w = recv_meta[:, 1].contiguous().view(torch.float32)
-        row_expert = recv_row_experts(recv_counts)
+        row_expert = recv_row_experts(recv_counts, R)
         nbytes = lib.fr_moe_experts_workspace_bytes(R, H, I, El)
         ws = _lib.workspace(nbytes, dev, "ep_experts")
         rc = lib.fr_moe_experts_peer(ctypes_ptr(pb.x_ptrs), H, W, pb.rows, _lib.ptr(src_rank), _lib.ptr(src_row),
