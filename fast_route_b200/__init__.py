@@ -6,10 +6,10 @@ operator surface; ``parallel`` adds expert parallelism over NCCL.
 """
 
 from . import _lib
-from .layers.stable_route import fused_moe
+from .layers.stable_route import fused_moe, fused_experts
 from .layers.host import fused_moe_host
 from .ops.stable_route import fused_route, route_from_logits
 from .ops.fused_moe import moe_align_block_size, invoke_fused_moe_kernel
 
-__all__ = ["fused_moe", "fused_moe_host", "fused_route", "route_from_logits", "moe_align_block_size",
+__all__ = ["fused_moe", "fused_experts", "fused_moe_host", "fused_route", "route_from_logits", "moe_align_block_size",
            "invoke_fused_moe_kernel", "_lib"]

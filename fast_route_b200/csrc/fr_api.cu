@@ -695,6 +695,29 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
   return experts_impl(x, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st);
 }
 
+int fr_moe_layer_routed(const void* x, const int32_t* topk_ids, const float* topk_weights, const void* w1,
+                        const void* w2, int dtype, int64_t M, int H, int I, int E, int topk, void* out,
+                        void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !topk_ids || !w1 || !w2 || !out || M < 0 || H <= 0 || I <= 0 || E <= 0 || topk <= 0) return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (I % 8)) return FR_ERR_ALIGN;
+  if (M == 0) return FR_OK;
+  if (!workspace || workspace_bytes < fr_moe_workspace_bytes(M, H, I, E, topk)) return FR_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
+  Carver c(workspace);
+  void* aws;
+  size_t aws_bytes;
+  carve_align_ws(c, E, &aws, &aws_bytes);
+  carve_route(c, M, H, E, topk);
+  c.take<float>(M * topk);
+  c.take<int32_t>(M * topk);
+  ExpertWs ews = carve_experts(c, M * topk, H, I, E);
+  ews.align_ws = aws;
+  ews.align_ws_bytes = aws_bytes;
+  return experts_impl(x, H, topk_ids, topk_weights, w1, w2, dtype, M, topk, H, I, E, out, H, ews,
+                      static_cast<cudaStream_t>(stream));
+}
+
 size_t fr_moe_experts_workspace_bytes(int64_t R, int H, int I, int E_local) {
   if (R <= 0 || H <= 0 || I <= 0 || E_local <= 0) return 0;
   Carver c(nullptr);

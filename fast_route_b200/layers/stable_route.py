@@ -48,3 +48,34 @@ def fused_moe(hidden_states: torch.Tensor, gate: torch.Tensor, w1: torch.Tensor,
                           ws.numel(), _lib.stream_ptr(dev))
     _lib.check(rc, "fr_moe_layer")
     return (out, tw, ti) if return_routing else out
+
+
+def fused_experts(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_weights: torch.Tensor,
+                  topk_ids: torch.Tensor, inplace: bool = False) -> torch.Tensor:
+    """The expert part of the layer for a routing computed elsewhere, with the argument order of the
+    vLLM-style ``fused_moe(hidden_states, w1, w2, topk_weights, topk_ids, inplace)`` that the reference
+    benchmarks against (``benchmarks/swizzle_moe/v0_moe_fused.py:219-224``).  ``topk_weights`` /
+    ``topk_ids`` are ``[M, topk]`` of any float / integer dtype and any strides (they are compacted to
+    fp32 / int32 here, which also removes the reference's strided-view pitfall)."""
+    assert hidden_states.shape[1] == w1.shape[2], "Incompatible dimensions"
+    assert hidden_states.is_contiguous() and w1.is_contiguous() and w2.is_contiguous()
+    assert hidden_states.dtype in [torch.float16, torch.bfloat16]
+    assert topk_weights.shape == topk_ids.shape
+    _lib.require_cuda(hidden_states, w1, w2, topk_weights, topk_ids)
+    M, H = hidden_states.shape
+    E, N, _ = w1.shape
+    I = N // 2
+    topk = topk_ids.shape[1]
+    tw = topk_weights.to(torch.float32).contiguous()
+    ti = topk_ids.to(torch.int32).contiguous()
+    out = hidden_states if inplace else torch.empty_like(hidden_states)
+    if M == 0:
+        return out
+    lib = _lib.load()
+    dev = hidden_states.device
+    ws = _lib.workspace(lib.fr_moe_workspace_bytes(M, H, I, E, topk), dev, "layer")
+    rc = lib.fr_moe_layer_routed(_lib.ptr(hidden_states), _lib.ptr(ti), _lib.ptr(tw), _lib.ptr(w1), _lib.ptr(w2),
+                                 _lib.dtype_code(hidden_states.dtype), M, H, I, E, topk, _lib.ptr(out), _lib.ptr(ws),
+                                 ws.numel(), _lib.stream_ptr(dev))
+    _lib.check(rc, "fr_moe_layer_routed")
+    return out

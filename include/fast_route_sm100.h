@@ -169,6 +169,15 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
                  float* topk_weights_out, int32_t* topk_ids_out, void* workspace, size_t workspace_bytes,
                  void* stream);
 
+/* The layer for a routing computed elsewhere: align -> permute -> GEMM1+SiLU -> GEMM2 -> combine with
+ * the caller's compact topk_ids[M,topk] (int32) and topk_weights[M,topk] (fp32, may be NULL = 1).
+ * Stands in for the vLLM-style signature fused_moe(hidden_states, w1, w2, topk_weights, topk_ids)
+ * that the reference benchmarks against (benchmarks/swizzle_moe/v0_moe_fused.py:219-224,
+ * benchmarks/swizzle_moe/perf_test_moe.py:48-58).  Workspace as fr_moe_layer. */
+int fr_moe_layer_routed(const void* x, const int32_t* topk_ids, const float* topk_weights, const void* w1,
+                        const void* w2, int dtype, int64_t M, int H, int I, int E, int topk, void* out,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 /* Expert-parallel building blocks (no counterpart in the reference, which is single-GPU).
  * fr_moe_experts: the expert part of the layer for rows that already carry an expert id
  * (tokens received from other ranks): align by local expert -> permute -> GEMM1+SiLU ->

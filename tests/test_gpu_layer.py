@@ -230,3 +230,19 @@ def test_host_buffer_entry_point_matches_device_layer(dev):
     out2 = fr.fused_moe_host(xh, gd, w1d, w2d, k, chunk=4096)
     torch.cuda.synchronize()
     assert torch.equal(out2, ref.cpu())
+
+
+@pytest.mark.parametrize("m,n,k,e,topk,dt", [(33, 128, 256, 8, 2, torch.float16), (512, 384, 512, 16, 4, torch.bfloat16),
+                                             (2000, 256, 256, 64, 6, torch.float16)])
+def test_fused_experts_given_routing(dev, m, n, k, e, topk, dt):
+    """The reference's own layer test (benchmarks/swizzle_moe/perf_test_moe.py:33-68): randn/10 tensors,
+    routing from softmax scores + torch.topk, compared with torch_moe at atol 1e-2."""
+    g = torch.Generator().manual_seed(3227)
+    a = (torch.randn(m, k, generator=g) / 10).to(dt)
+    w1 = (torch.randn(e, 2 * n, k, generator=g) / 10).to(dt)
+    w2 = (torch.randn(e, k, n, generator=g) / 10).to(dt)
+    score = torch.softmax(torch.randn(m, e, generator=g).to(dt).float(), dim=-1)
+    topk_weight, topk_ids = torch.topk(score, topk)
+    out = fr.fused_experts(a.to(dev), w1.to(dev), w2.to(dev), topk_weight.to(dev), topk_ids.to(dev))
+    ref = oracle.torch_moe(a.float(), w1.float(), w2.float(), topk_weight.float(), topk_ids)
+    torch.testing.assert_close(out.float().cpu(), ref, atol=1e-2, rtol=0)
