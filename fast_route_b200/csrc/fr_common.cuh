@@ -69,18 +69,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every spin in this library is bounded.  try_wait itself suspends the thread for a
-// hardware-defined slice, so the budget below is many seconds of wall time; a healthy
-// pipeline needs a handful of iterations.  On expiry: record, and let the caller unwind.
+// Every spin in this library is bounded: waits are try_wait loops with an iteration budget.
+// try_wait itself suspends the thread for a hardware-defined slice, so the budget below is
+// seconds of wall time; a healthy pipeline needs a handful of iterations.
 constexpr uint32_t kWaitBudget = 1u << 24;
-
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, unsigned int where) {
-  for (uint32_t it = 0; it < kWaitBudget; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-  }
-  report(ST_WAIT_TIMEOUT, where);
-  return false;
-}
 
 // ----------------------------------------------------------------------------------
 // TMA (cp.async.bulk.tensor), 2-D tiles, no multicast anywhere in this library.
@@ -96,32 +88,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
       : "memory");
 }
-__device__ __forceinline__ void tma_load_2d_hint(void* smem_dst, const CUtensorMap* m, uint64_t* bar, int c0,
-                                                 int c1, uint64_t policy) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
-      "[%0], [%1, {%3, %4}], [%2], %5;"
-      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1),
-      "l"(policy)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* m, const void* smem_src, int c0, int c1) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                   reinterpret_cast<uint64_t>(m)),
-               "r"(smem_u32(smem_src)), "r"(c0), "r"(c1)
-               : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-
 // ----------------------------------------------------------------------------------
 // tcgen05 / TMEM, cta_group::1
 // ----------------------------------------------------------------------------------

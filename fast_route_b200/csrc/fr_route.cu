@@ -72,7 +72,6 @@ __global__ void __launch_bounds__(256) topk_softmax_kernel(const T* __restrict__
     if (c0 + i >= E) v[i] = -INFINITY;
   }
 
-  // running max / sum over all columns, only needed without renormalisation
   float sel_v[KMAX];
   int sel_c[KMAX];
   uint32_t taken = 0;

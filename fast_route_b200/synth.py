@@ -9,8 +9,6 @@ see identical bits.
 
 from __future__ import annotations
 
-import math
-
 import torch
 
 
@@ -100,5 +98,4 @@ def layer_bytes(active_experts: int, M: int, H: int, I: int, E: int, elt: int = 
     return active_experts * 3.0 * H * I * elt + 2.0 * M * H * elt + H * E * elt
 
 
-__all__ = ["randn", "moe_inputs", "zipf_gate_bias", "routing_logits", "layer_flops",
-           "layer_bytes", "math"]
+__all__ = ["randn", "moe_inputs", "zipf_gate_bias", "routing_logits", "layer_flops", "layer_bytes"]
