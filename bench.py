@@ -235,6 +235,27 @@ def sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms):
     return rows
 
 
+def transformer_block(fr, wg, w1, w2, M, H, k):
+    """Mixtral-style block tail: h = attn_out + x; out = h + moe(rmsnorm(h) * gamma).  Fused (one C call:
+    add+norm kernel, residual inside the combine kernel) against the same math with framework ops around
+    the layer."""
+    dev, dt = w1.device, w1.dtype
+    attn = torch.randn(M, H, device=dev, dtype=dt) * 0.5
+    x = torch.randn(M, H, device=dev, dtype=dt)
+    gamma = torch.ones(H, device=dev, dtype=dt)
+
+    def fused():
+        return fr.moe_block(attn, x, wg.t(), w1, w2, k, gamma=gamma, add_residual=True)
+
+    def unfused():
+        h = attn + x
+        u = torch.nn.functional.rms_norm(h, (H,), gamma, 1e-5)
+        return h + fr.fused_moe(u, wg.t(), w1, w2, k)
+    f_ms, _ = cuda_time_ms(fused, 8)
+    u_ms, _ = cuda_time_ms(unfused, 8)
+    return {"tokens": M, "ms_fused_block": f_ms, "ms_layer_plus_framework_ops": u_ms}
+
+
 def routing_latency(fr, synth, dev):
     from fast_route_b200 import _lib
     lib = _lib.load()
@@ -457,6 +478,7 @@ def run_ours(args, rank, world, local_rank):
             Ms = [m for m in (1, 4, 16, 64, 256, 1024, 4096, 16384)]
             line["sweep"] = sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms)
             line["routing_latency"] = routing_latency(fr, synth, dev)
+            line["transformer_block"] = transformer_block(fr, wg, w1, w2, M, H, k)
         if not args.no_cpu:
             cb = cpu_reference_rate(H, I, E, k, args.cpu_tokens, 3, warm=1, weights=(wg, w1, w2), budget_s=20.0)
             line["cpu_baseline"] = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}

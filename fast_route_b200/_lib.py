@@ -41,6 +41,9 @@ SIGNATURES = {
     "fr_combine": (_I, [_P, _L, _I, _P, _L, _I, _I, _L, _P, _L, _P]),
     "fr_moe_workspace_bytes": (_Z, [_L, _I, _I, _I, _I]),
     "fr_moe_layer": (_I, [_P, _P, _L, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _Z, _P]),
+    "fr_add_rmsnorm": (_I, [_P, _L, _P, _L, _P, ctypes.c_float, _I, _L, _I, _P, _L, _P, _L, _P]),
+    "fr_moe_block_workspace_bytes": (_Z, [_L, _I, _I, _I, _I]),
+    "fr_moe_block": (_I, [_P, _P, _P, ctypes.c_float, _P, _L, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _Z, _P]),
     "fr_moe_layer_routed": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _I, _P, _P, _Z, _P]),
     "fr_moe_experts_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fr_moe_experts": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _P, _Z, _P]),

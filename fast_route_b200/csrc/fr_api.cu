@@ -21,7 +21,8 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
                           cudaStream_t st, int* deferred_split);
 int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, const float* topk_w,
-                             int64_t M, int topk, int dtype, void* out, int64_t ld_out, cudaStream_t st);
+                             int64_t M, int topk, int dtype, const void* residual, int64_t ld_res, void* out,
+                             int64_t ld_out, cudaStream_t st);
 int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate_km,
                          int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
                          int32_t* ids, float* logits_out, cudaStream_t st);
@@ -66,16 +67,28 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const uint4* __restric
   }
 }
 
-// out[t,:] = sum_j y[inv_pos[t*topk+j], :], fp32 accumulation in slot order, one rounding.
+// out[t,:] = (residual[t,:] +) sum_j y[inv_pos[t*topk+j], :], fp32 accumulation in slot order, one
+// rounding.  out may alias residual (each thread reads its residual vector before storing it).
 template <bool BF16>
 __global__ void __launch_bounds__(256) combine_kernel(const uint4* __restrict__ y, int64_t ld_y_v,
                                                       const int32_t* __restrict__ inv_pos, int topk, int row_v,
-                                                      int64_t max_rows, uint4* __restrict__ out, int64_t ld_out_v) {
+                                                      int64_t max_rows, const uint4* residual, int64_t ld_res_v,
+                                                      uint4* out, int64_t ld_out_v) {
   const int64_t t = blockIdx.x;
   for (int v = threadIdx.x; v < row_v; v += blockDim.x) {
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+    if (residual) {
+      const uint4 raw = residual[t * ld_res_v + v];
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = unpack2<BF16>(w[i]);
+        acc[2 * i] = f.x;
+        acc[2 * i + 1] = f.y;
+      }
+    }
     for (int j = 0; j < topk; ++j) {
       const int32_t pos = __ldg(inv_pos + t * topk + j);
       if (pos < 0 || pos >= max_rows) continue;
@@ -162,6 +175,77 @@ __global__ void __launch_bounds__(256) combine_peer_kernel(const uint4* const* _
     }
     out[t * ld_out_v + v] = make_uint4(pack2<BF16>(acc[0], acc[1]), pack2<BF16>(acc[2], acc[3]),
                                        pack2<BF16>(acc[4], acc[5]), pack2<BF16>(acc[6], acc[7]));
+  }
+}
+
+// Residual add and RMSNorm in one pass over the rows: h = a (+ b); x = h * rsqrt(mean(h^2) + eps) * gamma.
+// One CTA per row, 16-byte vectors, the row is held in registers between the two phases (H <= 16384).
+// h is rounded to the element type first and the norm is taken of the rounded values, as a framework
+// that materialises h would do.  h_out and x_out are optional; without gamma, x_out = h.
+template <bool BF16>
+__global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint4* __restrict__ a, int64_t ld_a_v,
+                                                          const uint4* __restrict__ b, int64_t ld_b_v,
+                                                          const uint4* __restrict__ gamma, float eps, int H,
+                                                          uint4* __restrict__ h_out, int64_t ld_h_v,
+                                                          uint4* __restrict__ x_out, int64_t ld_x_v) {
+  constexpr int MAXV = 8;
+  __shared__ float red[8];
+  const int64_t row = blockIdx.x;
+  const int row_v = H / 8;
+  uint4 hv[MAXV];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < row_v) {
+      uint4 ra = __ldg(a + row * ld_a_v + v);
+      uint32_t w[4] = {ra.x, ra.y, ra.z, ra.w};
+      if (b) {
+        const uint4 rb = __ldg(b + row * ld_b_v + v);
+        const uint32_t wb[4] = {rb.x, rb.y, rb.z, rb.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 fa = unpack2<BF16>(w[q]), fb = unpack2<BF16>(wb[q]);
+          w[q] = pack2<BF16>(fa.x + fb.x, fa.y + fb.y);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack2<BF16>(w[q]);
+        ss = fmaf(f.x, f.x, ss);
+        ss = fmaf(f.y, f.y, ss);
+      }
+      hv[i] = make_uint4(w[0], w[1], w[2], w[3]);
+      if (h_out) h_out[row * ld_h_v + v] = hv[i];
+    }
+  }
+  if (!x_out) return;
+  float scale = 1.0f;
+  if (gamma) {
+    for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tot += red[w];
+    scale = rsqrtf(tot / static_cast<float>(H) + eps);
+  }
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < row_v) {
+      uint32_t w[4] = {hv[i].x, hv[i].y, hv[i].z, hv[i].w};
+      if (gamma) {
+        const uint4 rg = __ldg(gamma + v);
+        const uint32_t wg[4] = {rg.x, rg.y, rg.z, rg.w};
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = unpack2<BF16>(w[q]), g = unpack2<BF16>(wg[q]);
+          w[q] = pack2<BF16>(f.x * scale * g.x, f.y * scale * g.y);
+        }
+      }
+      x_out[row * ld_x_v + v] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
   }
 }
 
@@ -394,7 +478,8 @@ static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
 // token i / topk) whose expert ids are in `ids`.
 static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const float* weights, const void* w1,
                         const void* w2, int dtype, int64_t M, int topk, int H, int I, int E, void* out,
-                        int64_t ld_out, const ExpertWs& w, cudaStream_t st) {
+                        int64_t ld_out, const ExpertWs& w, cudaStream_t st, const void* residual = nullptr,
+                        int64_t ld_res = 0) {
   const int64_t n = M * topk;
   int rc = align_dispatch(ids, n, E, kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len, w.num_post,
                           nullptr, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
@@ -412,15 +497,16 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
                              weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred);
   if (rc) return rc;
   if (deferred > 1)  // split-K GEMM2: its reduction, the routed weights and the sum over slots in one kernel
-    return combine_partial_dispatch(w.split, deferred, n, H, weights, M, topk, dtype, out, ld_out, st);
+    return combine_partial_dispatch(w.split, deferred, n, H, weights, M, topk, dtype, residual, ld_res, out, ld_out,
+                                    st);
   if (dtype == FR_BF16)
     combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
         reinterpret_cast<const uint4*>(w.y_sorted), H / 8, w.inv_pos, topk, row_v, w.rows,
-        static_cast<uint4*>(out), ld_out / 8);
+        static_cast<const uint4*>(residual), ld_res / 8, static_cast<uint4*>(out), ld_out / 8);
   else
     combine_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(
         reinterpret_cast<const uint4*>(w.y_sorted), H / 8, w.inv_pos, topk, row_v, w.rows,
-        static_cast<uint4*>(out), ld_out / 8);
+        static_cast<const uint4*>(residual), ld_res / 8, static_cast<uint4*>(out), ld_out / 8);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -643,12 +729,12 @@ int fr_combine(const void* y, int64_t ld_y, int dtype, const int32_t* inv_pos, i
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (dtype == FR_BF16)
     combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(static_cast<const uint4*>(y), ld_y / 8, inv_pos,
-                                                                   topk, H / 8, max_rows, static_cast<uint4*>(out),
-                                                                   ld_out / 8);
+                                                                   topk, H / 8, max_rows, nullptr, 0,
+                                                                   static_cast<uint4*>(out), ld_out / 8);
   else
     combine_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(static_cast<const uint4*>(y), ld_y / 8, inv_pos,
-                                                                    topk, H / 8, max_rows, static_cast<uint4*>(out),
-                                                                    ld_out / 8);
+                                                                    topk, H / 8, max_rows, nullptr, 0,
+                                                                    static_cast<uint4*>(out), ld_out / 8);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -693,6 +779,83 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
                             nullptr, rws, st);
   if (rc) return rc;
   return experts_impl(x, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st);
+}
+
+int fr_add_rmsnorm(const void* a, int64_t ld_a, const void* b, int64_t ld_b, const void* gamma, float eps, int dtype,
+                   int64_t M, int H, void* h_out, int64_t ld_h, void* x_out, int64_t ld_x, void* stream) {
+  if (!a || M < 0 || H <= 0 || (!h_out && !x_out)) return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if (H > 8 * 8 * 256) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (ld_a % 8) || (b && (ld_b % 8)) || (h_out && (ld_h % 8)) || (x_out && (ld_x % 8)))
+    return FR_ERR_ALIGN;
+  for (const void* p : {a, b, gamma, static_cast<const void*>(h_out), static_cast<const void*>(x_out)})
+    if (p && (reinterpret_cast<uintptr_t>(p) & 15)) return FR_ERR_ALIGN;
+  if (M == 0) return FR_OK;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (dtype == FR_BF16)
+    add_rmsnorm_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
+        static_cast<const uint4*>(a), ld_a / 8, static_cast<const uint4*>(b), ld_b / 8,
+        static_cast<const uint4*>(gamma), eps, H, static_cast<uint4*>(h_out), ld_h / 8, static_cast<uint4*>(x_out),
+        ld_x / 8);
+  else
+    add_rmsnorm_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(
+        static_cast<const uint4*>(a), ld_a / 8, static_cast<const uint4*>(b), ld_b / 8,
+        static_cast<const uint4*>(gamma), eps, H, static_cast<uint4*>(h_out), ld_h / 8, static_cast<uint4*>(x_out),
+        ld_x / 8);
+  return static_cast<int>(cudaGetLastError());
+}
+
+size_t fr_moe_block_workspace_bytes(int64_t M, int H, int I, int E, int topk) {
+  if (M <= 0 || H <= 0) return 0;
+  return fr_moe_workspace_bytes(M, H, I, E, topk) + ((static_cast<size_t>(M) * H * 2 + 1023) & ~size_t(1023)) * 2;
+}
+
+int fr_moe_block(const void* attn_out, const void* x, const void* gamma, float eps, const void* gate,
+                 int64_t gate_stride_h, int64_t gate_stride_e, const void* w1, const void* w2, int dtype, int64_t M,
+                 int H, int I, int E, int topk, int renormalize, int add_residual, void* out, void* workspace,
+                 size_t workspace_bytes, void* stream) {
+  if (!attn_out || !gate || !w1 || !w2 || !out || M < 0 || H <= 0 || I <= 0 || E <= 0 || topk <= 0 || topk > E)
+    return FR_ERR_ARG;
+  if (M == 0) return FR_OK;
+  if (!workspace || workspace_bytes < fr_moe_block_workspace_bytes(M, H, I, E, topk)) return FR_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
+  // layer workspace first (its align scratch must stay at offset 0), then h and the normalised input
+  const size_t layer_bytes = fr_moe_workspace_bytes(M, H, I, E, topk);
+  const size_t row_bytes = (static_cast<size_t>(M) * H * 2 + 1023) & ~size_t(1023);
+  uint8_t* base = static_cast<uint8_t*>(workspace);
+  void* h = base + layer_bytes;
+  void* u = base + layer_bytes + row_bytes;
+  const bool need_h = (x != nullptr);   // without x, h is attn_out itself
+  const void* moe_in = attn_out;
+  const void* res = nullptr;
+  if (gamma) {
+    int rc = fr_add_rmsnorm(attn_out, H, x, H, gamma, eps, dtype, M, H, need_h ? h : nullptr, H, u, H, stream);
+    if (rc) return rc;
+    moe_in = u;
+    res = add_residual ? (need_h ? h : attn_out) : nullptr;
+  } else if (x) {  // no norm: the experts read h itself
+    int rc = fr_add_rmsnorm(attn_out, H, x, H, nullptr, eps, dtype, M, H, h, H, nullptr, H, stream);
+    if (rc) return rc;
+    moe_in = h;
+    res = add_residual ? h : nullptr;
+  } else if (add_residual) {
+    res = attn_out;
+  }
+  Carver c(workspace);
+  void* aws;
+  size_t aws_bytes;
+  carve_align_ws(c, E, &aws, &aws_bytes);
+  RouteWs rws = carve_route(c, M, H, E, topk);
+  float* tw = c.take<float>(M * topk);
+  int32_t* ti = c.take<int32_t>(M * topk);
+  ExpertWs ews = carve_experts(c, M * topk, H, I, E);
+  ews.align_ws = aws;
+  ews.align_ws_bytes = aws_bytes;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = route_fused_impl(moe_in, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
+                            nullptr, rws, st);
+  if (rc) return rc;
+  return experts_impl(moe_in, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st, res, H);
 }
 
 int fr_moe_layer_routed(const void* x, const int32_t* topk_ids, const float* topk_weights, const void* w1,

@@ -349,12 +349,17 @@ splitk_reduce_weighted_kernel(const float* __restrict__ partial, int64_t partial
 template <bool BF16>
 __global__ void __launch_bounds__(256)
 combine_partial_kernel(const float* __restrict__ partial, int64_t partial_cols, int split_k, int64_t n_valid,
-                       const float* __restrict__ topk_w, int topk, int H, uint16_t* __restrict__ out,
-                       int64_t ld_out) {
+                       const float* __restrict__ topk_w, int topk, int H, const uint16_t* __restrict__ residual,
+                       int64_t ld_res, uint16_t* __restrict__ out, int64_t ld_out) {
   const int64_t t = blockIdx.y;
   const int j = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (j >= H) return;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (residual) {  // read before the store below: out may alias residual
+    const uint2 r = *reinterpret_cast<const uint2*>(residual + t * ld_res + j);
+    const float2 r0 = unpack2<BF16>(r.x), r1 = unpack2<BF16>(r.y);
+    acc = make_float4(r0.x, r0.y, r1.x, r1.y);
+  }
   for (int q = 0; q < topk; ++q) {
     const int64_t sid = t * topk + q;
     const float w = topk_w ? __ldg(topk_w + sid) : 1.0f;
@@ -550,17 +555,20 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
 }
 
 int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, const float* topk_w,
-                             int64_t M, int topk, int dtype, void* out, int64_t ld_out, cudaStream_t st) {
+                             int64_t M, int topk, int dtype, const void* residual, int64_t ld_res, void* out,
+                             int64_t ld_out, cudaStream_t st) {
   const int64_t partial_cols = static_cast<int64_t>((n_out + GEMM_BN - 1) / GEMM_BN) * GEMM_BN;
   const dim3 grid(static_cast<unsigned>((n_out + 1023) / 1024), static_cast<unsigned>(M));
   if (dtype == FR_BF16)
     combine_partial_kernel<true><<<grid, 256, 0, st>>>(static_cast<const float*>(workspace), partial_cols, split_k,
-                                                       n_valid, topk_w, topk, n_out, static_cast<uint16_t*>(out),
-                                                       ld_out);
+                                                       n_valid, topk_w, topk, n_out,
+                                                       static_cast<const uint16_t*>(residual), ld_res,
+                                                       static_cast<uint16_t*>(out), ld_out);
   else
     combine_partial_kernel<false><<<grid, 256, 0, st>>>(static_cast<const float*>(workspace), partial_cols, split_k,
-                                                        n_valid, topk_w, topk, n_out, static_cast<uint16_t*>(out),
-                                                        ld_out);
+                                                        n_valid, topk_w, topk, n_out,
+                                                        static_cast<const uint16_t*>(residual), ld_res,
+                                                        static_cast<uint16_t*>(out), ld_out);
   return static_cast<int>(cudaGetLastError());
 }
 

@@ -169,6 +169,22 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
                  float* topk_weights_out, int32_t* topk_ids_out, void* workspace, size_t workspace_bytes,
                  void* stream);
 
+/* Transformer-block glue around the layer (the reference's block is h = attn(x) + x; fused_moe(h),
+ * benchmarks/fused_route/transformerLayer_bench.py:66-79; Mixtral adds an RMSNorm and a second residual).
+ * fr_add_rmsnorm: h = a (+ b);  x = h * rsqrt(mean(h^2) + eps) * gamma, one pass over the rows.
+ * b, gamma, h_out, x_out are optional (without gamma x_out = h).  H <= 16384.
+ * fr_moe_block:  h = attn_out (+ x);  u = gamma ? rmsnorm(h) * gamma : h;
+ *                out = (add_residual ? h : 0) + moe(u)
+ * as one launch sequence: the add and the norm are one kernel, the second residual is added inside
+ * the combine kernel (fp32, one rounding).  out may alias attn_out or x. */
+int fr_add_rmsnorm(const void* a, int64_t ld_a, const void* b, int64_t ld_b, const void* gamma, float eps, int dtype,
+                   int64_t M, int H, void* h_out, int64_t ld_h, void* x_out, int64_t ld_x, void* stream);
+size_t fr_moe_block_workspace_bytes(int64_t M, int H, int I, int E, int topk);
+int fr_moe_block(const void* attn_out, const void* x, const void* gamma, float eps, const void* gate,
+                 int64_t gate_stride_h, int64_t gate_stride_e, const void* w1, const void* w2, int dtype, int64_t M,
+                 int H, int I, int E, int topk, int renormalize, int add_residual, void* out, void* workspace,
+                 size_t workspace_bytes, void* stream);
+
 /* The layer for a routing computed elsewhere: align -> permute -> GEMM1+SiLU -> GEMM2 -> combine with
  * the caller's compact topk_ids[M,topk] (int32) and topk_weights[M,topk] (fp32, may be NULL = 1).
  * Stands in for the vLLM-style signature fused_moe(hidden_states, w1, w2, topk_weights, topk_ids)

@@ -246,3 +246,59 @@ def test_fused_experts_given_routing(dev, m, n, k, e, topk, dt):
     out = fr.fused_experts(a.to(dev), w1.to(dev), w2.to(dev), topk_weight.to(dev), topk_ids.to(dev))
     ref = oracle.torch_moe(a.float(), w1.float(), w2.float(), topk_weight.float(), topk_ids)
     torch.testing.assert_close(out.float().cpu(), ref, atol=1e-2, rtol=0)
+
+
+def _rmsnorm_ref(h, gamma, eps):
+    hf = h.float()
+    return (hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * gamma.float()).to(h.dtype)
+
+
+@pytest.mark.parametrize("M,H,dt", [(1, 64, torch.bfloat16), (37, 4096, torch.bfloat16), (300, 2048, torch.float16),
+                                    (5, 16384, torch.bfloat16), (64, 1032, torch.float16)])
+def test_add_rmsnorm(dev, M, H, dt):
+    a = synth.randn((M, H), 31, 0).to(dt).to(dev)
+    b = synth.randn((M, H), 31, 1).to(dt).to(dev)
+    gamma = (1.0 + 0.1 * synth.randn((H,), 31, 2)).to(dt).to(dev)
+    h, x = fr.add_rmsnorm(a, b, gamma, 1e-5)
+    href = (a.float() + b.float()).to(dt)
+    assert torch.equal(h, href)
+    xref = _rmsnorm_ref(href, gamma, 1e-5)
+    assert (x.float() - xref.float()).abs().max().item() <= 2.0 ** -6 * max(1.0, xref.float().abs().max().item())
+    h2, x2 = fr.add_rmsnorm(a, None, gamma, 1e-5, want_h=False)
+    assert h2 is None and (x2.float() - _rmsnorm_ref(a, gamma, 1e-5).float()).abs().max().item() <= 0.05
+    h3, x3 = fr.add_rmsnorm(a, b)
+    assert torch.equal(h3, href) and x3 is h3
+
+
+@pytest.mark.parametrize("M,H,I,E,k,dt,norm,resid", [(200, 512, 384, 8, 2, torch.bfloat16, False, False),
+                                                     (200, 512, 384, 8, 2, torch.bfloat16, True, True),
+                                                     (3, 1024, 512, 8, 2, torch.float16, True, True),
+                                                     (1000, 256, 640, 16, 4, torch.bfloat16, True, False),
+                                                     (64, 512, 768, 8, 2, torch.bfloat16, False, True)])
+def test_moe_block(dev, M, H, I, E, k, dt, norm, resid):
+    """h = attn_out + x; u = rmsnorm(h)*gamma (optional); out = (h +) moe(u).  norm=False, resid=False is the
+    reference's block (benchmarks/fused_route/transformerLayer_bench.py:66-79)."""
+    x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=14, dtype=dt, weight_std=0.05)
+    attn = (synth.randn((M, H), 14, 50) * 0.5).to(dt)
+    gamma = (1.0 + 0.1 * synth.randn((H,), 14, 51)).to(dt) if norm else None
+    gd, w1d, w2d = gate.to(dev), w1.to(dev), w2.to(dev)
+    out = fr.moe_block(attn.to(dev), x.to(dev), gd, w1d, w2d, k, gamma=None if gamma is None else gamma.to(dev),
+                       add_residual=resid)
+    h = (attn.float() + x.float()).to(dt)
+    u = _rmsnorm_ref(h, gamma, 1e-5) if norm else h
+    # the block must equal the layer applied to the same u (bit for bit without the residual)
+    base = fr.fused_moe(u.to(dev), gd, w1d, w2d, k)
+    if not resid:
+        assert (out.float() - base.float()).abs().max().item() <= (2.0 ** -6 if norm else 0.0) * max(1.0, base.float().abs().max().item())
+    tw, ti = fr.fused_route(u.to(dev), gd, k)
+    ref, _, _ = oracle.moe_layer(u, gate, w1, w2, k, routing=(tw.cpu(), ti.cpu()))
+    if resid:
+        ref = ref + h.float()
+    diff = (out.float().cpu() - ref).abs()
+    assert diff.max().item() <= MAX_ABS + ref.abs().max().item() * 2.0 ** -7
+    assert (diff.mean() / ref.abs().mean()).item() <= MEAN_REL
+    # in place on the attention output
+    a2 = attn.to(dev).clone()
+    out2 = fr.moe_block(a2, x.to(dev), gd, w1d, w2d, k, gamma=None if gamma is None else gamma.to(dev),
+                        add_residual=resid, out=a2)
+    assert out2.data_ptr() == a2.data_ptr() and torch.equal(out2, out)
