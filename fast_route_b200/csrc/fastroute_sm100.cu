@@ -3,4 +3,5 @@
 #include "fr_route.cu"
 #include "fr_route_coop.cu"
 #include "fr_gemm.cu"
+#include "fr_gemm_tokenn.cu"
 #include "fr_api.cu"

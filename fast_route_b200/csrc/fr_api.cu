@@ -20,9 +20,13 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
                           cudaStream_t st, int* deferred_split);
-int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, const float* topk_w,
-                             int64_t M, int topk, int dtype, const void* residual, int64_t ld_res, void* out,
-                             int64_t ld_out, cudaStream_t st);
+int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, int64_t partial_cols,
+                             const float* topk_w, int64_t M, int topk, int dtype, const void* residual,
+                             int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st);
+int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, int dtype, int64_t max_rows, int K,
+                         int n_out, int E, int w_rows_per_expert, const int32_t* counts, const int32_t* num_post,
+                         const int32_t* sorted_ids, const float* topk_w, int64_t n_valid, void* out, int64_t ldo,
+                         int split_k, void* workspace, size_t workspace_bytes, cudaStream_t st, int* deferred_split);
 int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate_km,
                          int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
                          int32_t* ids, float* logits_out, cudaStream_t st);
@@ -387,6 +391,32 @@ static SplitPlan plan_split(int64_t n, int H, int I, int E) {
   return sp;
 }
 
+// Token-N path (fr_gemm_tokenn.cu): used while an expert sees at most this many tokens on average.
+// Its small token operand leaves room for up to 10 pipeline stages of weights (160 KB in flight per
+// SM against 128 KB in the row-block kernel), which is what a weight-streaming batch needs; with
+// 256-token tiles only a third of the in-flight bytes are weights and the row-block kernel wins.
+// (measured on B200, Mixtral-8x7B shape: 3-13 % faster up to 128 tokens per expert, slower from 256)
+constexpr int64_t kTokenNMaxTokensPerExpert = 128;
+constexpr int kTokenNMaxExperts = 256;
+static bool use_tokenn(int64_t n, int E) { return E <= kTokenNMaxExperts && n <= kTokenNMaxTokensPerExpert * E; }
+
+static SplitPlan plan_split_tokenn(int64_t n, int H, int I, int E) {
+  SplitPlan sp;
+  if (n <= 0) return sp;
+  const int sms = sm_count_or_default();
+  const int64_t avg = (n + E - 1) / E;
+  int box = 16;
+  while (box < 256 && box < 2 * avg) box <<= 1;
+  const int64_t est_tt = (n < E ? n : E) + n / box;  // token tiles: one per active expert + full ones
+  const int wt1 = (I + 63) / 64, wt2 = (H + 127) / 128;
+  sp.s1 = choose_split_k(est_tt * wt1, (H + kTileK - 1) / kTileK, sms);
+  sp.s2 = choose_split_k(est_tt * wt2, (I + kTileK - 1) / kTileK, sms);
+  size_t b1 = sp.s1 > 1 ? static_cast<size_t>(sp.s1) * n * wt1 * 128 * sizeof(float) : 0;
+  size_t b2 = sp.s2 > 1 ? static_cast<size_t>(sp.s2) * n * wt2 * 128 * sizeof(float) : 0;
+  sp.bytes = b1 > b2 ? b1 : b2;
+  return sp;
+}
+
 struct RouteWs {
   uint16_t* gate_km;
   float* logits;
@@ -439,7 +469,7 @@ static int route_fused_impl(const void* x, int dtype, int64_t M, int H, int64_t 
 }
 
 struct ExpertWs {
-  int32_t *sorted, *expert_ids, *num_post, *inv_pos;
+  int32_t *sorted, *expert_ids, *num_post, *inv_pos, *counts;
   uint16_t *a_sorted, *act, *y_sorted;
   void* split;
   void* align_ws;
@@ -461,15 +491,16 @@ static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
   w.align_ws_bytes = 0;
   w.rows = rows_cap(n, E);
   w.sorted_len = round_up(n + static_cast<int64_t>(E) * (kBlockM - 1), kBlockM);
-  w.expert_ids_len = w.sorted_len / kBlockM + 1;
+  w.expert_ids_len = w.sorted_len / 16 + 1;   // block -> expert table, sized for the 16-row alignment
   w.sorted = c.take<int32_t>(w.sorted_len);
   w.expert_ids = c.take<int32_t>(w.expert_ids_len);
   w.num_post = c.take<int32_t>(4);
   w.inv_pos = c.take<int32_t>(n);
+  w.counts = c.take<int32_t>(E);
   w.a_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
   w.act = c.take<uint16_t>(static_cast<size_t>(w.rows) * I);
   w.y_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
-  w.sp = plan_split(n, H, I, E);
+  w.sp = use_tokenn(n, E) ? plan_split_tokenn(n, H, I, E) : plan_split(n, H, I, E);
   w.split = c.take<uint8_t>(w.sp.bytes);
   return w;
 }
@@ -481,24 +512,39 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
                         int64_t ld_out, const ExpertWs& w, cudaStream_t st, const void* residual = nullptr,
                         int64_t ld_res = 0) {
   const int64_t n = M * topk;
-  int rc = align_dispatch(ids, n, E, kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len, w.num_post,
-                          nullptr, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
+  const bool tokenn = use_tokenn(n, E);
+  int rc = align_dispatch(ids, n, E, tokenn ? 16 : kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
+                          w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
   if (rc) return rc;
   const int row_v = H / 8;
   permute_rows_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
       static_cast<const uint4*>(x), ldx / 8, w.sorted, w.num_post, n, topk, reinterpret_cast<uint4*>(w.a_sorted),
       H / 8, row_v);
   FR_CUDA_OK(cudaGetLastError());
-  rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
-                             w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
-  if (rc) return rc;
-  int deferred = 0;
-  rc = gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
-                             weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred);
-  if (rc) return rc;
-  if (deferred > 1)  // split-K GEMM2: its reduction, the routed weights and the sum over slots in one kernel
-    return combine_partial_dispatch(w.split, deferred, n, H, weights, M, topk, dtype, residual, ld_res, out, ld_out,
-                                    st);
+  if (tokenn) {
+    // few tokens per expert: tokens on the MMA N axis, experts padded to 16 rows instead of 128
+    rc = gemm_tokenn_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.counts, w.num_post, w.sorted,
+                              nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
+    if (rc) return rc;
+    int deferred = 0;
+    rc = gemm_tokenn_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.counts, w.num_post, w.sorted, weights, n,
+                              w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred);
+    if (rc) return rc;
+    if (deferred > 1)
+      return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + 127) / 128) * 128, weights, M,
+                                      topk, dtype, residual, ld_res, out, ld_out, st);
+  } else {
+    rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
+                               w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
+    if (rc) return rc;
+    int deferred = 0;
+    rc = gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
+                               weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred);
+    if (rc) return rc;
+    if (deferred > 1)  // split-K GEMM2: its reduction, the routed weights and the sum over slots in one kernel
+      return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + kTileN - 1) / kTileN) * kTileN,
+                                      weights, M, topk, dtype, residual, ld_res, out, ld_out, st);
+  }
   if (dtype == FR_BF16)
     combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
         reinterpret_cast<const uint4*>(w.y_sorted), H / 8, w.inv_pos, topk, row_v, w.rows,

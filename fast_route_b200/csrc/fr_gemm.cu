@@ -53,6 +53,12 @@ struct PipeState {
       phase ^= 1;
     }
   }
+  __device__ __forceinline__ void advance_rt(uint32_t stages) {
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
 };
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
@@ -554,10 +560,9 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
             : launch_grouped<MODE_WEIGHTED, false>(tmA, tmB, p, grid, st);
 }
 
-int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, const float* topk_w,
-                             int64_t M, int topk, int dtype, const void* residual, int64_t ld_res, void* out,
-                             int64_t ld_out, cudaStream_t st) {
-  const int64_t partial_cols = static_cast<int64_t>((n_out + GEMM_BN - 1) / GEMM_BN) * GEMM_BN;
+int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, int64_t partial_cols,
+                             const float* topk_w, int64_t M, int topk, int dtype, const void* residual,
+                             int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st) {
   const dim3 grid(static_cast<unsigned>((n_out + 1023) / 1024), static_cast<unsigned>(M));
   if (dtype == FR_BF16)
     combine_partial_kernel<true><<<grid, 256, 0, st>>>(static_cast<const float*>(workspace), partial_cols, split_k,
