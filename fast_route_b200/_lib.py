@@ -44,6 +44,8 @@ SIGNATURES = {
     "fr_add_rmsnorm": (_I, [_P, _L, _P, _L, _P, ctypes.c_float, _I, _L, _I, _P, _L, _P, _L, _P]),
     "fr_moe_block_workspace_bytes": (_Z, [_L, _I, _I, _I, _I]),
     "fr_moe_block": (_I, [_P, _P, _P, ctypes.c_float, _P, _L, _L, _P, _P, _I, _L, _I, _I, _I, _I, _I, _I, _P, _P, _Z, _P]),
+    "fr_moe_fp8_workspace_bytes": (_Z, [_L, _I, _I, _I, _I]),
+    "fr_moe_layer_fp8": (_I, [_P, _P, _L, _L, _P, _P, _P, _P, _I, _L, _I, _I, _I, _I, _I, _P, _P, _P, _P, _Z, _P]),
     "fr_moe_layer_routed": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _I, _P, _P, _Z, _P]),
     "fr_moe_experts_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fr_moe_experts": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _P, _Z, _P]),

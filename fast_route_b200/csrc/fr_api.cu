@@ -1,6 +1,8 @@
 // C ABI of libfastroute_sm100.so: argument checks, workspace carving, the memory-bound
 // helper kernels (row permute / gather, combine, gate transpose) and the whole-layer
 // launch sequence.  See include/fast_route_sm100.h for the contract of every entry point.
+#include <cuda_fp8.h>
+
 #include "fr_common.cuh"
 
 namespace fr {
@@ -19,14 +21,15 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st, int* deferred_split);
+                          cudaStream_t st, int* deferred_split, const QuantArgs* quant);
 int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, int64_t partial_cols,
                              const float* topk_w, int64_t M, int topk, int dtype, const void* residual,
                              int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st);
 int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, int dtype, int64_t max_rows, int K,
                          int n_out, int E, int w_rows_per_expert, const int32_t* counts, const int32_t* num_post,
                          const int32_t* sorted_ids, const float* topk_w, int64_t n_valid, void* out, int64_t ldo,
-                         int split_k, void* workspace, size_t workspace_bytes, cudaStream_t st, int* deferred_split);
+                         int split_k, void* workspace, size_t workspace_bytes, cudaStream_t st, int* deferred_split,
+                         const QuantArgs* quant);
 int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate_km,
                          int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
                          int32_t* ids, float* logits_out, cudaStream_t st);
@@ -251,6 +254,90 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(const uint4* __restric
       x_out[row * ld_x_v + v] = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
+}
+
+// ----------------------------------------------------------------------------------
+// fp8 (E4M3) activations: one scale per row, scale = absmax / 448, value = round(v / scale)
+// ----------------------------------------------------------------------------------
+__device__ __forceinline__ uint2 quant8_e4m3(const float (&v)[8], float scale) {
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const uint32_t a = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[4 * i], scale), __fdiv_rn(v[4 * i + 1], scale)),
+                                                __NV_SATFINITE, __NV_E4M3);
+    const uint32_t b = __nv_cvt_float2_to_fp8x2(
+        make_float2(__fdiv_rn(v[4 * i + 2], scale), __fdiv_rn(v[4 * i + 3], scale)), __NV_SATFINITE, __NV_E4M3);
+    const uint32_t w = a | (b << 16);
+    if (i == 0) lo = w; else hi = w;
+  }
+  return make_uint2(lo, hi);
+}
+
+// Shared body: the CTA holds one row (up to 8 vectors of 8 elements per thread), finds its absmax,
+// writes the fp8 row and the scale.  src == nullptr writes a zero row with scale 1.
+template <bool BF16>
+__device__ __forceinline__ void quant_row(const uint4* __restrict__ src, int row_v, uint2* __restrict__ dst,
+                                          float* __restrict__ scale_out) {
+  constexpr int MAXV = 8;
+  __shared__ float red[8];
+  float vals[MAXV][8];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < row_v && src) {
+      const uint4 raw = __ldg(src + v);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 f = unpack2<BF16>(w[q]);
+        vals[i][2 * q] = f.x;
+        vals[i][2 * q + 1] = f.y;
+        amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) vals[i][q] = 0.0f;
+    }
+  }
+  for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  float tot = 0.0f;
+#pragma unroll
+  for (int w = 0; w < 8; ++w) tot = fmaxf(tot, red[w]);
+  const float scale = tot > 0.0f ? __fdiv_rn(tot, 448.0f) : 1.0f;
+  if (threadIdx.x == 0) *scale_out = scale;
+#pragma unroll
+  for (int i = 0; i < MAXV; ++i) {
+    const int v = threadIdx.x + i * 256;
+    if (v < row_v) dst[v] = quant8_e4m3(vals[i], scale);
+  }
+}
+
+// a_q[p,:] = fp8(x[sorted_ids[p] / topk, :]) with its row scale: the gather of the fp8 layer
+template <bool BF16>
+__global__ void __launch_bounds__(256) permute_quant_rows_kernel(const uint4* __restrict__ src, int64_t ld_src_v,
+                                                                 const int32_t* __restrict__ sorted_ids,
+                                                                 const int32_t* __restrict__ num_post, int64_t n,
+                                                                 int topk, uint2* __restrict__ dst, int64_t ld_dst_v,
+                                                                 float* __restrict__ row_scale, int row_v) {
+  const int64_t row = blockIdx.x;
+  if (row >= __ldg(num_post)) return;
+  const int32_t sid = __ldg(sorted_ids + row);
+  const uint4* s = (sid >= 0 && sid < n) ? src + static_cast<int64_t>(sid / topk) * ld_src_v : nullptr;
+  quant_row<BF16>(s, row_v, dst + row * ld_dst_v, row_scale + row);
+}
+
+// act_q[p,:] = fp8(act[p,:]) with its row scale, for the rows in use
+template <bool BF16>
+__global__ void __launch_bounds__(256) quant_rows_kernel(const uint4* __restrict__ src, int64_t ld_src_v,
+                                                         const int32_t* __restrict__ num_post,
+                                                         uint2* __restrict__ dst, int64_t ld_dst_v,
+                                                         float* __restrict__ row_scale, int row_v) {
+  const int64_t row = blockIdx.x;
+  if (row >= __ldg(num_post)) return;
+  quant_row<BF16>(src + row * ld_src_v, row_v, dst + row * ld_dst_v, row_scale + row);
 }
 
 // Router for a handful of rows (decode-sized batches): one CTA per token, the H-long dot
@@ -501,6 +588,10 @@ static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
   w.act = c.take<uint16_t>(static_cast<size_t>(w.rows) * I);
   w.y_sorted = c.take<uint16_t>(static_cast<size_t>(w.rows) * H);
   w.sp = use_tokenn(n, E) ? plan_split_tokenn(n, H, I, E) : plan_split(n, H, I, E);
+  {  // the scratch also covers the row-block plan (used by the fp8 layer at every batch size)
+    const size_t rb = plan_split(n, H, I, E).bytes;
+    if (rb > w.sp.bytes) w.sp.bytes = rb;
+  }
   w.split = c.take<uint8_t>(w.sp.bytes);
   return w;
 }
@@ -524,22 +615,22 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
   if (tokenn) {
     // few tokens per expert: tokens on the MMA N axis, experts padded to 16 rows instead of 128
     rc = gemm_tokenn_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.counts, w.num_post, w.sorted,
-                              nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
+                              nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, nullptr);
     if (rc) return rc;
     int deferred = 0;
     rc = gemm_tokenn_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.counts, w.num_post, w.sorted, weights, n,
-                              w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred);
+                              w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred, nullptr);
     if (rc) return rc;
     if (deferred > 1)
       return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + 127) / 128) * 128, weights, M,
                                       topk, dtype, residual, ld_res, out, ld_out, st);
   } else {
     rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
-                               w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
+                               w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, nullptr);
     if (rc) return rc;
     int deferred = 0;
     rc = gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
-                               weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred);
+                               weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred, nullptr);
     if (rc) return rc;
     if (deferred > 1)  // split-K GEMM2: its reduction, the routed weights and the sum over slots in one kernel
       return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + kTileN - 1) / kTileN) * kTileN,
@@ -573,10 +664,10 @@ static int experts_peer_impl(const void* const* peer_x, int64_t ld_x, int world,
       w.num_post, R, reinterpret_cast<uint4*>(w.a_sorted), H / 8, H / 8);
   FR_CUDA_OK(cudaGetLastError());
   rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
-                             w.sorted, nullptr, R, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr);
+                             w.sorted, nullptr, R, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, nullptr);
   if (rc) return rc;
   return gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
-                               row_weight, R, y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, nullptr);
+                               row_weight, R, y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, nullptr, nullptr);
 }
 
 }  // namespace fr
@@ -752,7 +843,7 @@ int fr_gemm1_silu(const void* a_sorted, int64_t lda, const void* w1, int dtype, 
                   void* stream) {
   return gemm_grouped_dispatch(0, a_sorted, lda, w1, dtype, max_rows, H, I, E, 2 * I, expert_ids,
                                num_tokens_post_pad, sorted_ids, nullptr, n, act, ld_act, split_k, workspace,
-                               workspace_bytes, static_cast<cudaStream_t>(stream), nullptr);
+                               workspace_bytes, static_cast<cudaStream_t>(stream), nullptr, nullptr);
 }
 
 int fr_gemm2(const void* act, int64_t ld_act, const void* w2, int dtype, int64_t max_rows, int H, int I, int E,
@@ -761,7 +852,7 @@ int fr_gemm2(const void* act, int64_t ld_act, const void* w2, int dtype, int64_t
              size_t workspace_bytes, void* stream) {
   return gemm_grouped_dispatch(1, act, ld_act, w2, dtype, max_rows, I, H, E, H, expert_ids, num_tokens_post_pad,
                                sorted_ids, topk_weights, n, y, ld_y, split_k, workspace, workspace_bytes,
-                               static_cast<cudaStream_t>(stream), nullptr);
+                               static_cast<cudaStream_t>(stream), nullptr, nullptr);
 }
 
 int fr_combine(const void* y, int64_t ld_y, int dtype, const int32_t* inv_pos, int64_t M, int topk, int H,
@@ -902,6 +993,129 @@ int fr_moe_block(const void* attn_out, const void* x, const void* gamma, float e
                             nullptr, rws, st);
   if (rc) return rc;
   return experts_impl(moe_in, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st, res, H);
+}
+
+// ---- fp8 (E4M3) expert weights ---------------------------------------------------------------
+struct Fp8Ws {
+  uint8_t *a_q, *act_q;
+  float *a_scale, *act_scale;
+};
+static size_t carve_fp8_layer(Carver& c, int64_t M, int H, int I, int E, int topk, void** aws, size_t* aws_bytes,
+                              RouteWs* rws, float** tw, int32_t** ti, ExpertWs* ews, Fp8Ws* f8) {
+  carve_align_ws(c, E, aws, aws_bytes);
+  *rws = carve_route(c, M, H, E, topk);
+  *tw = c.take<float>(M * topk);
+  *ti = c.take<int32_t>(M * topk);
+  *ews = carve_experts(c, M * topk, H, I, E);
+  f8->a_q = c.take<uint8_t>(static_cast<size_t>(ews->rows) * H);
+  f8->act_q = c.take<uint8_t>(static_cast<size_t>(ews->rows) * I);
+  f8->a_scale = c.take<float>(ews->rows);
+  f8->act_scale = c.take<float>(ews->rows);
+  return c.total();
+}
+
+size_t fr_moe_fp8_workspace_bytes(int64_t M, int H, int I, int E, int topk) {
+  if (M <= 0 || H <= 0 || I <= 0 || E <= 0 || topk <= 0) return 0;
+  Carver c(nullptr);
+  void* aws;
+  size_t ab;
+  RouteWs rws;
+  float* tw;
+  int32_t* ti;
+  ExpertWs ews;
+  Fp8Ws f8;
+  return carve_fp8_layer(c, M, H, I, E, topk, &aws, &ab, &rws, &tw, &ti, &ews, &f8);
+}
+
+int fr_moe_layer_fp8(const void* x, const void* gate, int64_t gate_stride_h, int64_t gate_stride_e, const void* w1_q,
+                     const float* w1_scale, const void* w2_q, const float* w2_scale, int dtype, int64_t M, int H, int I,
+                     int E, int topk, int renormalize, void* out, float* topk_weights_out, int32_t* topk_ids_out,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  if (!x || !gate || !w1_q || !w1_scale || !w2_q || !w2_scale || !out || M < 0 || H <= 0 || I <= 0 || E <= 0 ||
+      topk <= 0 || topk > E)
+    return FR_ERR_ARG;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 16) || (I % 16)) return FR_ERR_ALIGN;
+  if (H > 16384 || I > 16384) return FR_ERR_UNSUPPORTED;  // a row is quantised by one CTA holding it in registers
+  if (M == 0) return FR_OK;
+  if (!workspace || workspace_bytes < fr_moe_fp8_workspace_bytes(M, H, I, E, topk)) return FR_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  Carver c(workspace);
+  void* aws;
+  size_t ab;
+  RouteWs rws;
+  float* tw;
+  int32_t* ti;
+  ExpertWs w;
+  Fp8Ws f8;
+  carve_fp8_layer(c, M, H, I, E, topk, &aws, &ab, &rws, &tw, &ti, &w, &f8);
+  w.align_ws = aws;
+  w.align_ws_bytes = ab;
+  if (topk_weights_out) tw = topk_weights_out;
+  if (topk_ids_out) ti = topk_ids_out;
+  int rc = route_fused_impl(x, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
+                            nullptr, rws, st);
+  if (rc) return rc;
+  const int64_t n = M * topk;
+  const bool tokenn = use_tokenn(n, E);
+  rc = align_dispatch(ti, n, E, tokenn ? 16 : kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
+                      w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
+  if (rc) return rc;
+  const bool bf = dtype == FR_BF16;
+  const unsigned rows = static_cast<unsigned>(w.rows);
+  if (bf)
+    permute_quant_rows_kernel<true><<<rows, 256, 0, st>>>(static_cast<const uint4*>(x), H / 8, w.sorted, w.num_post, n,
+                                                          topk, reinterpret_cast<uint2*>(f8.a_q), H / 8, f8.a_scale,
+                                                          H / 8);
+  else
+    permute_quant_rows_kernel<false><<<rows, 256, 0, st>>>(static_cast<const uint4*>(x), H / 8, w.sorted, w.num_post,
+                                                           n, topk, reinterpret_cast<uint2*>(f8.a_q), H / 8,
+                                                           f8.a_scale, H / 8);
+  FR_CUDA_OK(cudaGetLastError());
+  QuantArgs q1{f8.a_scale, w1_scale};
+  QuantArgs q2{f8.act_scale, w2_scale};
+  auto quant_act = [&]() -> int {
+    if (bf)
+      quant_rows_kernel<true><<<rows, 256, 0, st>>>(reinterpret_cast<const uint4*>(w.act), I / 8, w.num_post,
+                                                    reinterpret_cast<uint2*>(f8.act_q), I / 8, f8.act_scale, I / 8);
+    else
+      quant_rows_kernel<false><<<rows, 256, 0, st>>>(reinterpret_cast<const uint4*>(w.act), I / 8, w.num_post,
+                                                     reinterpret_cast<uint2*>(f8.act_q), I / 8, f8.act_scale, I / 8);
+    return static_cast<int>(cudaGetLastError());
+  };
+  int deferred = 0;
+  int64_t partial_cols = 0;
+  if (tokenn) {
+    rc = gemm_tokenn_dispatch(0, f8.a_q, H, w1_q, dtype, w.rows, H, I, E, 2 * I, w.counts, w.num_post, w.sorted, nullptr,
+                              n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, &q1);
+    if (rc) return rc;
+    if ((rc = quant_act())) return rc;
+    rc = gemm_tokenn_dispatch(1, f8.act_q, I, w2_q, dtype, w.rows, I, H, E, H, w.counts, w.num_post, w.sorted, tw, n,
+                              w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred, &q2);
+    if (rc) return rc;
+    partial_cols = static_cast<int64_t>((H + 127) / 128) * 128;
+  } else {
+    rc = gemm_grouped_dispatch(0, f8.a_q, H, w1_q, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post, w.sorted,
+                               nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, &q1);
+    if (rc) return rc;
+    if ((rc = quant_act())) return rc;
+    rc = gemm_grouped_dispatch(1, f8.act_q, I, w2_q, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted, tw,
+                               n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred, &q2);
+    if (rc) return rc;
+    partial_cols = static_cast<int64_t>((H + kTileN - 1) / kTileN) * kTileN;
+  }
+  if (deferred > 1)
+    return combine_partial_dispatch(w.split, deferred, n, H, partial_cols, tw, M, topk, dtype, nullptr, 0, out, H, st);
+  if (bf)
+    combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.y_sorted), H / 8,
+                                                                   w.inv_pos, topk, H / 8, w.rows, nullptr, 0,
+                                                                   static_cast<uint4*>(out), H / 8);
+  else
+    combine_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.y_sorted), H / 8,
+                                                                    w.inv_pos, topk, H / 8, w.rows, nullptr, 0,
+                                                                    static_cast<uint4*>(out), H / 8);
+  return static_cast<int>(cudaGetLastError());
 }
 
 int fr_moe_layer_routed(const void* x, const int32_t* topk_ids, const float* topk_weights, const void* w1,

@@ -120,6 +120,18 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t a_desc, uin
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with 8-bit floating-point inputs (kind::f8f6f4; the formats are in the instruction descriptor).
+__device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp gets row (lane base + t).
@@ -165,6 +177,17 @@ __host__ __device__ constexpr uint32_t umma_idesc_f16(bool bf16, int M, int N) {
   return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
          (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
+
+// Instruction descriptor, kind::f8f6f4 with both inputs E4M3 (format code 0), fp32 accumulator, K-major.
+__host__ __device__ constexpr uint32_t umma_idesc_e4m3(int M, int N) {
+  return (1u << 4) | (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
+}
+
+// Dequantisation factors of the fp8 path: value = fp8 * row_scale[row] * col_scale[expert row of the weight].
+struct QuantArgs {
+  const float* row_scale;  // [sorted rows] activation scale per row
+  const float* col_scale;  // [E * weight rows per expert] weight scale per output channel
+};
 
 // ----------------------------------------------------------------------------------
 // small numeric helpers
@@ -227,10 +250,10 @@ struct DeviceInfo {
 };
 const DeviceInfo& device_info();
 
-// 2-D row-major tensor map: inner extent `cols` elements of 2 bytes, `rows` rows, row
+// 2-D row-major tensor map: inner extent `cols` elements of `elt_bytes` (2 or 1) bytes, `rows` rows, row
 // pitch `ld_elems` elements; box = box_cols x box_rows; 128-byte swizzle.
 int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
-                 uint32_t box_rows, uint32_t box_cols, bool swizzle128);
+                 uint32_t box_rows, uint32_t box_cols, bool swizzle128, int elt_bytes = 2);
 
 #define FR_CUDA_OK(expr)                         \
   do {                                           \

@@ -42,6 +42,8 @@ struct GemmParams {
   int split_k;
   int kb_per_split;
   int group_m;
+  const float* row_scale;  // fp8 inputs only: activation scale per sorted row
+  const float* col_scale;  // fp8 inputs only: weight scale per weight row (E * b_rows_per_expert)
 };
 
 struct PipeState {
@@ -81,7 +83,9 @@ struct GemmSmem {
   static constexpr int TOTAL = STAGES * (A_STAGE_BYTES + B_STAGE_BYTES) + BAR_BYTES + 1024;  // + alignment slack
 };
 
-template <int BN, int STAGES, int MODE, bool BF16>
+// FP8: A and B are E4M3 bytes (128 elements per 128-byte smem row, MMA K = 32) and the epilogue applies
+// row_scale[row] * col_scale[weight row]; the output / partial format is unchanged.
+template <int BN, int STAGES, int MODE, bool BF16, bool FP8 = false>
 __global__ void __launch_bounds__(192, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                     const GemmParams p) {
@@ -129,7 +133,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   if (num_mb > mb_cap) num_mb = mb_cap;
   const int per_split = num_mb * p.num_nb;
   const int tiles = per_split * p.split_k;
-  const int KB = (p.K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;  // elements per 128-byte row of a stage
+  const int KB = (p.K + BKE - 1) / BKE;
 
   auto decode = [&](int tile, int& mb, int& nb, int& kb0, int& kb1) {
     const int ks = tile / per_split;
@@ -161,13 +166,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             break;
           }
           mbar_expect_tx(&full[ps.stage], A_STAGE_BYTES + SM::B_STAGE_BYTES);
-          tma_load_2d(sA + ps.stage * A_STAGE_BYTES, &tmA, &full[ps.stage], kb * BK, mb * BM);
+          tma_load_2d(sA + ps.stage * A_STAGE_BYTES, &tmA, &full[ps.stage], kb * BKE, mb * BM);
           uint8_t* bdst = sB + ps.stage * SM::B_STAGE_BYTES;
           if (p.two_box) {
-            tma_load_2d(bdst, &tmB, &full[ps.stage], kb * BK, brow);
-            tma_load_2d(bdst + (BN / 2) * BK * 2, &tmB, &full[ps.stage], kb * BK, brow + p.b_half_offset);
+            tma_load_2d(bdst, &tmB, &full[ps.stage], kb * BKE, brow);
+            tma_load_2d(bdst + (BN / 2) * BK * 2, &tmB, &full[ps.stage], kb * BKE, brow + p.b_half_offset);
           } else {
-            tma_load_2d(bdst, &tmB, &full[ps.stage], kb * BK, brow);
+            tma_load_2d(bdst, &tmB, &full[ps.stage], kb * BKE, brow);
           }
           ps.advance<STAGES>();
         }
@@ -176,7 +181,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------ MMA issuer --------------------------------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(BF16, BM, BN);
+      constexpr uint32_t idesc = FP8 ? umma_idesc_e4m3(BM, BN) : umma_idesc_f16(BF16, BM, BN);
       PipeState ps;
       uint32_t it = 0;
       bool ok = true;
@@ -196,8 +201,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           const uint64_t adesc = umma_desc_sw128(smem_u32(sA + ps.stage * A_STAGE_BYTES));
           const uint64_t bdesc = umma_desc_sw128(smem_u32(sB + ps.stage * SM::B_STAGE_BYTES));
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {  // 4 MMAs per stage, 32 bytes of K each
+            if constexpr (FP8) tc_mma_f8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty[ps.stage]);  // frees the smem stage once these MMAs have read it
           ps.advance<STAGES>();
@@ -217,6 +223,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * BN;
+      float rs = 1.0f;
+      const float* cs = nullptr;  // weight scales of this tile's expert
+      if constexpr (FP8) {
+        rs = __ldg(p.row_scale + row);
+        cs = p.col_scale + static_cast<int64_t>(__ldg(p.expert_ids + mb)) * p.b_rows_per_expert;
+      }
 
       if constexpr (MODE == MODE_SILU) {
         constexpr int HALF = BN / 2;
@@ -229,12 +241,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tc_wait_ld();
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) {
-            const float a0 = silu_f(__uint_as_float(g[2 * i])) * __uint_as_float(u[2 * i]);
-            const float a1 = silu_f(__uint_as_float(g[2 * i + 1])) * __uint_as_float(u[2 * i + 1]);
-            pk[i] = pack2<BF16>(a0, a1);
-          }
           const int col = nb * HALF + c0;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float g0 = __uint_as_float(g[2 * i]), g1 = __uint_as_float(g[2 * i + 1]);
+            float u0 = __uint_as_float(u[2 * i]), u1 = __uint_as_float(u[2 * i + 1]);
+            if constexpr (FP8) {
+              const int c = min(col + 2 * i, p.n_out - 2);
+              g0 *= rs * __ldg(cs + c);
+              g1 *= rs * __ldg(cs + c + 1);
+              u0 *= rs * __ldg(cs + p.b_half_offset + c);
+              u1 *= rs * __ldg(cs + p.b_half_offset + c + 1);
+            }
+            pk[i] = pack2<BF16>(silu_f(g0) * u0, silu_f(g1) * u1);
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col + v * 8 + 8 <= p.n_out)
@@ -254,9 +274,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tc_wait_ld();
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            pk[i] = pack2<BF16>(w * __uint_as_float(a[2 * i]), w * __uint_as_float(a[2 * i + 1]));
           const int col = nb * BN + c0;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float a0 = w * __uint_as_float(a[2 * i]), a1 = w * __uint_as_float(a[2 * i + 1]);
+            if constexpr (FP8) {
+              const int c = min(col + 2 * i, p.n_out - 2);
+              a0 *= rs * __ldg(cs + c);
+              a1 *= rs * __ldg(cs + c + 1);
+            }
+            pk[i] = pack2<BF16>(a0, a1);
+          }
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
             if (col + v * 8 + 8 <= p.n_out)
@@ -276,6 +304,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld32(taddr + c0, a);
           tc_wait_ld();
           if (valid) {
+            if constexpr (FP8) {  // partial sums leave the kernel already dequantised
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                int c = c0 + i;  // column inside the tile -> weight row of the expert
+                int wr = p.two_box ? (c < BN / 2 ? nb * (BN / 2) + c : p.b_half_offset + nb * (BN / 2) + c - BN / 2)
+                                   : nb * BN + c;
+                wr = min(wr, p.b_rows_per_expert - 1);
+                a[i] = __float_as_uint(__uint_as_float(a[i]) * rs * __ldg(cs + wr));
+              }
+            }
 #pragma unroll
             for (int v = 0; v < 8; ++v) {
               if (static_cast<int64_t>(nb) * BN + c0 + v * 4 + 4 <= p.partial_cols)
@@ -401,15 +439,16 @@ static EncodeTiledFn encode_fn() {
 }
 
 int make_tmap_2d(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld_elems,
-                 uint32_t box_rows, uint32_t box_cols, bool swizzle128) {
+                 uint32_t box_rows, uint32_t box_cols, bool swizzle128, int elt_bytes) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return FR_ERR_DRIVER;
-  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld_elems * 2) & 15)) return FR_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || ((ld_elems * elt_bytes) & 15)) return FR_ERR_ALIGN;
   cuuint64_t gdim[2] = {cols, rows};
-  cuuint64_t gstride[1] = {ld_elems * 2};
+  cuuint64_t gstride[1] = {ld_elems * elt_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
   cuuint32_t estr[2] = {1, 1};
-  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+  CUresult r = fn(out, elt_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                  const_cast<void*>(base), gdim, gstride, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FR_OK : FR_ERR_DRIVER;
@@ -430,10 +469,10 @@ const DeviceInfo& device_info() {
 constexpr int GEMM_BN = 256;
 constexpr int GEMM_STAGES = 4;
 
-template <int MODE, bool BF16>
+template <int MODE, bool BF16, bool FP8 = false>
 static int launch_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
                           cudaStream_t st) {
-  auto kern = grouped_gemm_kernel<GEMM_BN, GEMM_STAGES, MODE, BF16>;
+  auto kern = grouped_gemm_kernel<GEMM_BN, GEMM_STAGES, MODE, BF16, FP8>;
   constexpr int smem = GemmSmem<GEMM_BN, GEMM_STAGES>::TOTAL;
   FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   kern<<<grid, 192, smem, st>>>(tmA, tmB, p);
@@ -462,7 +501,8 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st, int* deferred_split) {
+                          cudaStream_t st, int* deferred_split, const QuantArgs* quant) {
+  // quant != nullptr: a and w hold E4M3 bytes (lda and K count elements = bytes), dtype is the output type.
   // which: 0 = GEMM1 (two-box B, SiLU epilogue), 1 = GEMM2 (weighted epilogue).
   // deferred_split (GEMM2 only, may be null): when split-K is used, skip the reduction and
   // report the slice count; the caller then finishes with combine_partial_dispatch.
@@ -471,10 +511,13 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
     return FR_ERR_ARG;
   if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
   if (max_rows % BM) return FR_ERR_ARG;
-  if ((K % 8) || (n_out % 8) || (ldo % 8) || (lda % 8)) return FR_ERR_ALIGN;
+  const bool fp8 = quant != nullptr;
+  if (fp8 && (!quant->row_scale || !quant->col_scale)) return FR_ERR_ARG;
+  if ((K % (fp8 ? 16 : 8)) || (n_out % 8) || (ldo % 8) || (lda % (fp8 ? 16 : 8))) return FR_ERR_ALIGN;
   if (reinterpret_cast<uintptr_t>(out) & 15) return FR_ERR_ALIGN;
   if (split_k < 1) split_k = 1;
-  const int KB = (K + BK - 1) / BK;
+  const int BKE = fp8 ? 2 * BK : BK;
+  const int KB = (K + BKE - 1) / BKE;
   if (split_k > KB) split_k = KB;
   if ((which == 1 || split_k > 1) && !sorted_ids) return FR_ERR_ARG;
   const DeviceInfo& di = device_info();
@@ -491,6 +534,8 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
   p.K = K;
   p.n_out = n_out;
   p.b_rows_per_expert = b_rows_per_expert;
+  p.row_scale = fp8 ? quant->row_scale : nullptr;
+  p.col_scale = fp8 ? quant->col_scale : nullptr;
   p.two_box = (which == 0);
   p.b_half_offset = n_out;  // GEMM1: the linear ("up") branch starts I rows after the SiLU branch
   p.num_nb = p.two_box ? (n_out + GEMM_BN / 2 - 1) / (GEMM_BN / 2) : (n_out + GEMM_BN - 1) / GEMM_BN;
@@ -514,18 +559,22 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
 
   CUtensorMap tmA, tmB;
   int rc = make_tmap_2d(&tmA, a, static_cast<uint64_t>(max_rows), static_cast<uint64_t>(K),
-                        static_cast<uint64_t>(lda), BM, BK, true);
+                        static_cast<uint64_t>(lda), BM, BKE, true, fp8 ? 1 : 2);
   if (rc) return rc;
   rc = make_tmap_2d(&tmB, w, static_cast<uint64_t>(E) * b_rows_per_expert, static_cast<uint64_t>(K),
-                    static_cast<uint64_t>(K), p.two_box ? GEMM_BN / 2 : GEMM_BN, BK, true);
+                    static_cast<uint64_t>(K), p.two_box ? GEMM_BN / 2 : GEMM_BN, BKE, true, fp8 ? 1 : 2);
   if (rc) return rc;
 
   const int64_t max_tiles = (max_rows / BM) * p.num_nb * split_k;
   const int grid = static_cast<int>(max_tiles < di.sm_count ? max_tiles : di.sm_count);
   const bool bf = dtype == FR_BF16;
   if (split_k > 1) {
-    rc = bf ? launch_grouped<MODE_PARTIAL, true>(tmA, tmB, p, grid, st)
-            : launch_grouped<MODE_PARTIAL, false>(tmA, tmB, p, grid, st);
+    if (fp8)
+      rc = bf ? launch_grouped<MODE_PARTIAL, true, true>(tmA, tmB, p, grid, st)
+              : launch_grouped<MODE_PARTIAL, false, true>(tmA, tmB, p, grid, st);
+    else
+      rc = bf ? launch_grouped<MODE_PARTIAL, true>(tmA, tmB, p, grid, st)
+              : launch_grouped<MODE_PARTIAL, false>(tmA, tmB, p, grid, st);
     if (rc) return rc;
     if (which == 1 && deferred_split) {
       *deferred_split = split_k;
@@ -552,6 +601,13 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                                                                     static_cast<uint16_t*>(out), ldo);
     }
     return static_cast<int>(cudaGetLastError());
+  }
+  if (fp8) {
+    if (which == 0)
+      return bf ? launch_grouped<MODE_SILU, true, true>(tmA, tmB, p, grid, st)
+                : launch_grouped<MODE_SILU, false, true>(tmA, tmB, p, grid, st);
+    return bf ? launch_grouped<MODE_WEIGHTED, true, true>(tmA, tmB, p, grid, st)
+              : launch_grouped<MODE_WEIGHTED, false, true>(tmA, tmB, p, grid, st);
   }
   if (which == 0)
     return bf ? launch_grouped<MODE_SILU, true>(tmA, tmB, p, grid, st)

@@ -41,6 +41,8 @@ struct TokenNParams {
   int num_wt;                 // weight tiles per expert
   int split_k;
   int kb_per_split;
+  const float* row_scale;     // fp8 inputs only: activation scale per sorted row
+  const float* col_scale;     // fp8 inputs only: weight scale per weight row (E * w_rows_per_expert)
   int tn_box;                 // tokens per tile = TMA box height of the token operand: 16 ... 256
   int stages;                 // pipeline depth: TPIPE_BYTES / (16 KB + tn_box * 128 B), at most TMAX_STAGES
 };
@@ -52,7 +54,7 @@ struct TileInfo {
   int tn;        // MMA N: tokens rounded up to 16
 };
 
-template <int MODE, bool BF16>
+template <int MODE, bool BF16, bool FP8 = false>
 __global__ void __launch_bounds__(192, 1)
 tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
                    const TokenNParams p) {
@@ -111,7 +113,8 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int tiles = ex_tile0[p.E];
-  const int KB = (p.K + BK - 1) / BK;
+  constexpr int BKE = FP8 ? 2 * BK : BK;  // elements per 128-byte row of a stage
+  const int KB = (p.K + BKE - 1) / BKE;
 
   // tiles are visited in increasing order by every role: the expert pointer only moves forward
   auto decode = [&](int tile, int& e_ptr, TileInfo& t) {
@@ -148,9 +151,9 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
           mbar_expect_tx(&full[ps.stage], static_cast<uint32_t>(TW_STAGE_BYTES + TX_STAGE_BYTES));
           uint8_t* wdst = sW + ps.stage * TW_STAGE_BYTES;
-          tma_load_2d(wdst, &tmW, &full[ps.stage], kb * BK, wrow);
-          tma_load_2d(wdst + TW_STAGE_BYTES / 2, &tmW, &full[ps.stage], kb * BK, wrow + p.second_box_offset);
-          tma_load_2d(sX + ps.stage * TX_STAGE_BYTES, &tmX, &full[ps.stage], kb * BK, t.row0);
+          tma_load_2d(wdst, &tmW, &full[ps.stage], kb * BKE, wrow);
+          tma_load_2d(wdst + TW_STAGE_BYTES / 2, &tmW, &full[ps.stage], kb * BKE, wrow + p.second_box_offset);
+          tma_load_2d(sX + ps.stage * TX_STAGE_BYTES, &tmX, &full[ps.stage], kb * BKE, t.row0);
           ps.advance_rt(STAGES);
         }
       }
@@ -165,7 +168,7 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
         TileInfo t;
         decode(tile, e_ptr, t);
-        const uint32_t idesc = umma_idesc_f16(BF16, TW, t.tn);
+        const uint32_t idesc = FP8 ? umma_idesc_e4m3(TW, t.tn) : umma_idesc_f16(BF16, TW, t.tn);
         const int kb0 = t.ks * p.kb_per_split, kb1 = min(KB, kb0 + p.kb_per_split);
         const uint32_t buf = it & 1u, aphase = (it >> 1) & 1u;
         if (!wait_or_abort(&tempty[buf], aphase ^ 1, abort_flag, 0x601)) break;
@@ -180,8 +183,10 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           const uint64_t adesc = umma_desc_sw128(smem_u32(sW + ps.stage * TW_STAGE_BYTES));
           const uint64_t bdesc = umma_desc_sw128(smem_u32(sX + ps.stage * TX_STAGE_BYTES));
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k)
-            tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            if constexpr (FP8) tc_mma_f8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+          }
           tc_commit(&empty[ps.stage]);
           ps.advance_rt(STAGES);
         }
@@ -219,16 +224,29 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         const int tok = c * 32 + lane;
         const bool tok_ok = tok < t.tokens;
         const int64_t row = static_cast<int64_t>(t.row0) + tok;
+        float rs = 1.0f;
+        const float* cs = nullptr;  // weight scales of this tile's expert
+        if constexpr (FP8) {
+          rs = tok_ok ? __ldg(p.row_scale + row) : 0.0f;
+          cs = p.col_scale + static_cast<int64_t>(t.e) * p.w_rows_per_expert;
+        }
         if constexpr (MODE == MODE_SILU) {
           // features: lanes 0..63 of the tile are the SiLU rows, 64..127 the linear rows of the same outputs
           const int f0 = q * 16;
           uint32_t pk[8];
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            const float g0 = stage_tile[(f0 + 2 * i) * TSTAGE_STRIDE + lane];
-            const float g1 = stage_tile[(f0 + 2 * i + 1) * TSTAGE_STRIDE + lane];
-            const float u0 = stage_tile[(64 + f0 + 2 * i) * TSTAGE_STRIDE + lane];
-            const float u1 = stage_tile[(64 + f0 + 2 * i + 1) * TSTAGE_STRIDE + lane];
+            float g0 = stage_tile[(f0 + 2 * i) * TSTAGE_STRIDE + lane];
+            float g1 = stage_tile[(f0 + 2 * i + 1) * TSTAGE_STRIDE + lane];
+            float u0 = stage_tile[(64 + f0 + 2 * i) * TSTAGE_STRIDE + lane];
+            float u1 = stage_tile[(64 + f0 + 2 * i + 1) * TSTAGE_STRIDE + lane];
+            if constexpr (FP8) {
+              const int c = min(t.wt * 64 + f0 + 2 * i, p.n_out - 2);  // weight row of the SiLU branch
+              g0 *= rs * __ldg(cs + c);
+              g1 *= rs * __ldg(cs + c + 1);
+              u0 *= rs * __ldg(cs + p.second_box_offset + c);
+              u1 *= rs * __ldg(cs + p.second_box_offset + c + 1);
+            }
             pk[i] = pack2<BF16>(silu_f(g0) * u0, silu_f(g1) * u1);
           }
           const int col = t.wt * 64 + f0;
@@ -246,9 +264,16 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           }
           uint32_t pk[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            pk[i] = pack2<BF16>(w * stage_tile[(f0 + 2 * i) * TSTAGE_STRIDE + lane],
-                                w * stage_tile[(f0 + 2 * i + 1) * TSTAGE_STRIDE + lane]);
+          for (int i = 0; i < 16; ++i) {
+            float a0 = w * stage_tile[(f0 + 2 * i) * TSTAGE_STRIDE + lane];
+            float a1 = w * stage_tile[(f0 + 2 * i + 1) * TSTAGE_STRIDE + lane];
+            if constexpr (FP8) {
+              const int c = min(t.wt * 128 + f0 + 2 * i, p.n_out - 2);
+              a0 *= rs * __ldg(cs + c);
+              a1 *= rs * __ldg(cs + c + 1);
+            }
+            pk[i] = pack2<BF16>(a0, a1);
+          }
           const int col = t.wt * 128 + f0;
           if (tok_ok) {
             uint16_t* o = reinterpret_cast<uint16_t*>(p.out) + row * p.ldo + col;
@@ -271,6 +296,18 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
               val.y = stage_tile[(f0 + 4 * v + 1) * TSTAGE_STRIDE + lane];
               val.z = stage_tile[(f0 + 4 * v + 2) * TSTAGE_STRIDE + lane];
               val.w = stage_tile[(f0 + 4 * v + 3) * TSTAGE_STRIDE + lane];
+              if constexpr (FP8) {  // partial sums leave the kernel already dequantised
+                float* pv = &val.x;
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                  const int f = f0 + 4 * v + u;  // feature inside the tile -> weight row of the expert
+                  int wr = (p.features_per_tile == 64)
+                               ? (f < 64 ? t.wt * 64 + f : p.second_box_offset + t.wt * 64 + f - 64)
+                               : t.wt * 128 + f;
+                  wr = min(wr, p.w_rows_per_expert - 1);
+                  pv[u] *= rs * __ldg(cs + wr);
+                }
+              }
               *reinterpret_cast<float4*>(o + 4 * v) = val;
             }
           }
@@ -290,10 +327,10 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
 constexpr int TOKENN_SMEM = TPIPE_BYTES + TW * TSTAGE_STRIDE * 4 + (3 * TMAX_EXPERTS + 2) * 4 + 512 + 1024;
 
-template <int MODE, bool BF16>
+template <int MODE, bool BF16, bool FP8 = false>
 static int launch_tokenn(const CUtensorMap& tmW, const CUtensorMap& tmX, const TokenNParams& p, int grid,
                          cudaStream_t st) {
-  auto kern = tokenn_gemm_kernel<MODE, BF16>;
+  auto kern = tokenn_gemm_kernel<MODE, BF16, FP8>;
   FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TOKENN_SMEM));
   kern<<<grid, 192, TOKENN_SMEM, st>>>(tmW, tmX, p);
   return static_cast<int>(cudaGetLastError());
@@ -304,14 +341,18 @@ static int launch_tokenn(const CUtensorMap& tmW, const CUtensorMap& tmX, const T
 int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, int dtype, int64_t max_rows, int K,
                          int n_out, int E, int w_rows_per_expert, const int32_t* counts, const int32_t* num_post,
                          const int32_t* sorted_ids, const float* topk_w, int64_t n_valid, void* out, int64_t ldo,
-                         int split_k, void* workspace, size_t workspace_bytes, cudaStream_t st, int* deferred_split) {
+                         int split_k, void* workspace, size_t workspace_bytes, cudaStream_t st, int* deferred_split,
+                         const QuantArgs* quant) {
   if (deferred_split) *deferred_split = 0;
+  const bool fp8 = quant != nullptr;  // a and w hold E4M3 bytes; dtype is the output type
+  if (fp8 && (!quant->row_scale || !quant->col_scale)) return FR_ERR_ARG;
   if (!a || !w || !counts || !sorted_ids || !out || max_rows <= 0 || K <= 0 || n_out <= 0 || E <= 0) return FR_ERR_ARG;
   if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
   if (E > TMAX_EXPERTS) return FR_ERR_UNSUPPORTED;
-  if ((K % 8) || (n_out % 8) || (ldo % 8) || (lda % 8)) return FR_ERR_ALIGN;
+  if ((K % (fp8 ? 16 : 8)) || (n_out % 8) || (ldo % 8) || (lda % (fp8 ? 16 : 8))) return FR_ERR_ALIGN;
   if (reinterpret_cast<uintptr_t>(out) & 15) return FR_ERR_ALIGN;
-  const int KB = (K + BK - 1) / BK;
+  const int BKE = fp8 ? 2 * BK : BK;
+  const int KB = (K + BKE - 1) / BKE;
   if (split_k < 1) split_k = 1;
   if (split_k > KB) split_k = KB;
   const DeviceInfo& di = device_info();
@@ -326,6 +367,8 @@ int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, i
   p.E = E;
   p.K = K;
   p.n_out = n_out;
+  p.row_scale = fp8 ? quant->row_scale : nullptr;
+  p.col_scale = fp8 ? quant->col_scale : nullptr;
   p.w_rows_per_expert = w_rows_per_expert;
   p.features_per_tile = (which == 0) ? 64 : 128;
   p.second_box_offset = (which == 0) ? n_out : 64;
@@ -353,18 +396,22 @@ int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, i
   }
   CUtensorMap tmW, tmX;
   int rc = make_tmap_2d(&tmW, w, static_cast<uint64_t>(E) * w_rows_per_expert, static_cast<uint64_t>(K),
-                        static_cast<uint64_t>(K), 64, BK, true);
+                        static_cast<uint64_t>(K), 64, BKE, true, fp8 ? 1 : 2);
   if (rc) return rc;
   rc = make_tmap_2d(&tmX, a, static_cast<uint64_t>(max_rows), static_cast<uint64_t>(K), static_cast<uint64_t>(lda),
-                    static_cast<uint32_t>(p.tn_box), BK, true);
+                    static_cast<uint32_t>(p.tn_box), BKE, true, fp8 ? 1 : 2);
   if (rc) return rc;
   const int64_t active = n_valid < E ? n_valid : E;
   const int64_t max_tiles = (n_valid / p.tn_box + active) * p.num_wt * split_k;
   const int grid = static_cast<int>(max_tiles < di.sm_count ? (max_tiles > 0 ? max_tiles : 1) : di.sm_count);
   const bool bf = dtype == FR_BF16;
   if (split_k > 1) {
-    rc = bf ? launch_tokenn<MODE_PARTIAL, true>(tmW, tmX, p, grid, st)
-            : launch_tokenn<MODE_PARTIAL, false>(tmW, tmX, p, grid, st);
+    if (fp8)
+      rc = bf ? launch_tokenn<MODE_PARTIAL, true, true>(tmW, tmX, p, grid, st)
+              : launch_tokenn<MODE_PARTIAL, false, true>(tmW, tmX, p, grid, st);
+    else
+      rc = bf ? launch_tokenn<MODE_PARTIAL, true>(tmW, tmX, p, grid, st)
+              : launch_tokenn<MODE_PARTIAL, false>(tmW, tmX, p, grid, st);
     if (rc) return rc;
     if (which == 1 && deferred_split) {
       *deferred_split = split_k;
@@ -390,6 +437,13 @@ int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, i
                                                                     static_cast<uint16_t*>(out), ldo);
     }
     return static_cast<int>(cudaGetLastError());
+  }
+  if (fp8) {
+    if (which == 0)
+      return bf ? launch_tokenn<MODE_SILU, true, true>(tmW, tmX, p, grid, st)
+                : launch_tokenn<MODE_SILU, false, true>(tmW, tmX, p, grid, st);
+    return bf ? launch_tokenn<MODE_WEIGHTED, true, true>(tmW, tmX, p, grid, st)
+              : launch_tokenn<MODE_WEIGHTED, false, true>(tmW, tmX, p, grid, st);
   }
   if (which == 0)
     return bf ? launch_tokenn<MODE_SILU, true>(tmW, tmX, p, grid, st) : launch_tokenn<MODE_SILU, false>(tmW, tmX, p, grid, st);

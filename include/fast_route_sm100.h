@@ -185,6 +185,20 @@ int fr_moe_block(const void* attn_out, const void* x, const void* gamma, float e
                  int H, int I, int E, int topk, int renormalize, int add_residual, void* out, void* workspace,
                  size_t workspace_bytes, void* stream);
 
+/* The layer with 8-bit floating-point (E4M3) expert weights: w1_q[E,2I,H] and w2_q[E,H,I] hold E4M3
+ * bytes, w1_scale[E*2I] / w2_scale[E*H] one fp32 scale per weight row (weight = byte value * scale).
+ * Activations stay in `dtype` (FR_F16 / FR_BF16) at the interface; each row is quantised to E4M3 with
+ * its own scale (absmax / 448) while it is gathered, and again between the two GEMMs; both GEMMs run as
+ * tcgen05 kind::f8f6f4 MMAs with fp32 accumulation and the scales are applied in the epilogue.  Router,
+ * align and combine are those of fr_moe_layer.  H and I must be multiples of 16 and at most 16384.
+ * The reference only hints at this (commented-out "good config for fp8 inputs" autotune entries,
+ * fast_route/fast_route/ops/stable_route.py:20-28); it halves the weight bytes a small batch streams. */
+size_t fr_moe_fp8_workspace_bytes(int64_t M, int H, int I, int E, int topk);
+int fr_moe_layer_fp8(const void* x, const void* gate, int64_t gate_stride_h, int64_t gate_stride_e, const void* w1_q,
+                     const float* w1_scale, const void* w2_q, const float* w2_scale, int dtype, int64_t M, int H, int I,
+                     int E, int topk, int renormalize, void* out, float* topk_weights_out, int32_t* topk_ids_out,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
 /* The layer for a routing computed elsewhere: align -> permute -> GEMM1+SiLU -> GEMM2 -> combine with
  * the caller's compact topk_ids[M,topk] (int32) and topk_weights[M,topk] (fp32, may be NULL = 1).
  * Stands in for the vLLM-style signature fused_moe(hidden_states, w1, w2, topk_weights, topk_ids)
