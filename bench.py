@@ -217,13 +217,13 @@ def sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms):
         x = torch.randn(M, H, device=dev, dtype=w1.dtype)
         _, _, ti = fr.fused_moe(x, wg.t(), w1, w2, k, return_routing=True)
         active = int(torch.unique(ti).numel())
-        reps = 20 if M <= 1024 else 8
-        med, _ = cuda_time_ms(lambda: fr.fused_moe(x, wg.t(), w1, w2, k), reps)
+        reps = 50 if M <= 1024 else 8
+        med, _ = cuda_time_ms(lambda: fr.fused_moe(x, wg.t(), w1, w2, k), reps, warm=10 if M <= 1024 else 3)
         out = torch.empty_like(x)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             out = fr.fused_moe(x, wg.t(), w1, w2, k)
-        gmed, _ = cuda_time_ms(g.replay, reps)
+        gmed, _ = cuda_time_ms(g.replay, reps, warm=10 if M <= 1024 else 3)
         flops = synth.layer_flops(M, H, I, E, k)
         nbytes = synth.layer_bytes(active, M, H, I, E)
         rows.append({"M": M, "ms": round(med, 4), "ms_graph": round(gmed, 4), "tokens_per_s": M / gmed * 1e3,
