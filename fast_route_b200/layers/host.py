@@ -32,7 +32,7 @@ def _plan(M: int, chunk: int):
 
 
 def fused_moe_host(x_host: torch.Tensor, gate: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk: int,
-                   out_host: torch.Tensor = None, renormalize: bool = True, chunk: int = 4096) -> torch.Tensor:
+                   out_host: torch.Tensor = None, renormalize: bool = True, chunk: int = 6144) -> torch.Tensor:
     """``x_host[M,H]`` (pinned CPU memory, fp16/bf16) -> ``out_host[M,H]`` (pinned CPU memory).
 
     Weights and gate are device tensors as for ``fused_moe``.  The copies are asynchronous:
