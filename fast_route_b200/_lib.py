@@ -28,6 +28,7 @@ SIGNATURES = {
     "fr_error_string": (c_char_p, [_I]),
     "fr_check_status": (_I, [_P]),
     "fr_topk_softmax": (_I, [_P, _I, _L, _I, _L, _L, _I, _I, _P, _L, _P, _L, _I, _P]),
+    "fr_softmax_topk": (_I, [_P, _I, _L, _I, _L, _L, _I, _I, _P, _L, _P, _L, _P, _L, _P]),
     "fr_align_workspace_bytes": (_Z, [_I]),
     "fr_align": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _P, _P, _Z, _P]),
     "fr_align_noalloc": (_I, [_P, _L, _I, _I, _P, _L, _P, _L, _P, _P, _P, _P]),

@@ -706,6 +706,13 @@ int fr_topk_softmax(const void* logits, int dtype, int64_t M, int E, int64_t str
                                id_stride, fill_rest, static_cast<cudaStream_t>(stream));
 }
 
+int fr_softmax_topk(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e, int topk,
+                    int renormalize, float* weights, int64_t w_stride, int32_t* ids, int64_t id_stride,
+                    int32_t* source_rows, int64_t src_stride, void* stream) {
+  return fr::softmax_topk_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, renormalize, weights, w_stride, ids,
+                                   id_stride, source_rows, src_stride, static_cast<cudaStream_t>(stream));
+}
+
 size_t fr_align_workspace_bytes(int E) { return E > 0 ? coop_workspace_bytes(E) : 0; }
 
 int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids, int64_t sorted_len,

@@ -247,6 +247,152 @@ int topk_softmax_dispatch(const void* logits, int dtype, int64_t M, int E, int64
 }
 
 // ----------------------------------------------------------------------------------
+// Softmax over ALL E columns, then top-k on the probabilities: the routing of the reference's
+// baseline layer (fast_route/fast_route/layers/vllm_route.py:72-84), whose topk_softmax op comes from
+// vLLM 0.4.0 (csrc/moe/topk_softmax_kernels.cu there: softmax in fp32, k rounds of arg-max where
+// equal probabilities go to the lower expert id, source row = j*M + token).
+// Recipe, made of single IEEE fp32 operations so that a CPU checker can follow it bit by bit:
+//   e_c = exp_recipe(l_c - max_c l_c);  s = sums of 8 consecutive columns (ascending), combined by a
+//   balanced binary tree over adjacent blocks (E padded to a power of two >= 8 with exact zeros);
+//   p_c = e_c * (1 / s);  selection on p_c;  renormalize: w_j = p_j / ((p_0 + p_1) + ...).
+// ----------------------------------------------------------------------------------
+template <typename T, int L>
+__global__ void __launch_bounds__(256) softmax_topk_kernel(const T* __restrict__ logits, int64_t M, int E,
+                                                           int64_t stride_m, int64_t stride_e, int k,
+                                                           int renormalize, float* __restrict__ weights,
+                                                           int64_t w_stride, int32_t* __restrict__ ids,
+                                                           int64_t id_stride, int32_t* __restrict__ source_rows,
+                                                           int64_t src_stride) {
+  constexpr int VPL = 8;
+  const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const int64_t row = gthread / L;
+  const int sub = static_cast<int>(gthread % L);
+  const bool row_ok = row < M;
+  const int64_t r = row_ok ? row : (M - 1);
+  const int c0 = sub * VPL;
+  const T* src = logits + r * stride_m;
+
+  float v[VPL];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int c = c0 + i;
+    float x = (c < E) ? to_f32<T>(src[static_cast<int64_t>(c) * stride_e]) : -INFINITY;
+    if (x != x) x = -INFINITY;  // NaN is outside the contract; rank it last
+    v[i] = x;
+    mx = fmaxf(mx, x);
+  }
+#pragma unroll
+  for (int off = 1; off < L; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+
+  float part = 0.0f;
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    v[i] = (c0 + i < E) ? exp_recipe(__fsub_rn(v[i], mx)) : 0.0f;
+    part = (i == 0) ? v[0] : __fadd_rn(part, v[i]);
+  }
+#pragma unroll
+  for (int off = 1; off < L; off <<= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+  const float inv = __fdiv_rn(1.0f, part);
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) v[i] = (c0 + i < E) ? __fmul_rn(v[i], inv) : -INFINITY;
+
+  float sel_v[KMAX];
+  int sel_c[KMAX];
+  uint32_t taken = 0;
+#pragma unroll
+  for (int j = 0; j < KMAX; ++j) {
+    sel_v[j] = 0.0f;
+    sel_c[j] = 0;
+    if (j < k) {
+      float bv = -INFINITY;
+      int bc = 0x7fffffff;
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const bool free_slot = !((taken >> i) & 1u) && (c0 + i < E);
+        if (free_slot && beats(v[i], c0 + i, bv, bc)) {
+          bv = v[i];
+          bc = c0 + i;
+        }
+      }
+#pragma unroll
+      for (int off = L / 2; off > 0; off >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+        const int oc = __shfl_xor_sync(0xffffffffu, bc, off);
+        if (beats(ov, oc, bv, bc)) {
+          bv = ov;
+          bc = oc;
+        }
+      }
+      if (bc >= c0 && bc < c0 + VPL) taken |= 1u << (bc - c0);
+      sel_v[j] = bv;
+      sel_c[j] = bc;
+    }
+  }
+  float s = 1.0f;
+  if (renormalize) {
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j)
+      if (j < k) s = (j == 0) ? sel_v[0] : __fadd_rn(s, sel_v[j]);
+  }
+  if (row_ok) {
+#pragma unroll
+    for (int j = 0; j < KMAX; ++j) {
+      if (j < k && (j % L) == sub) {
+        weights[row * w_stride + j] = renormalize ? __fdiv_rn(sel_v[j], s) : sel_v[j];
+        ids[row * id_stride + j] = sel_c[j];
+        if (source_rows) source_rows[row * src_stride + j] = static_cast<int32_t>(j * M + row);
+      }
+    }
+  }
+}
+
+template <typename T>
+static int launch_softmax_topk(const void* logits, int64_t M, int E, int64_t stride_m, int64_t stride_e, int k,
+                               int renormalize, float* weights, int64_t w_stride, int32_t* ids, int64_t id_stride,
+                               int32_t* source_rows, int64_t src_stride, cudaStream_t st) {
+  const T* lp = static_cast<const T*>(logits);
+  const int threads = 256;
+#define FR_LAUNCH_SMTOPK(L_)                                                                                   \
+  do {                                                                                                        \
+    const int64_t total = M * (L_);                                                                           \
+    const unsigned blocks = static_cast<unsigned>((total + threads - 1) / threads);                           \
+    softmax_topk_kernel<T, L_><<<blocks, threads, 0, st>>>(lp, M, E, stride_m, stride_e, k, renormalize,      \
+                                                           weights, w_stride, ids, id_stride, source_rows,    \
+                                                           src_stride);                                       \
+  } while (0)
+  if (E <= 8) FR_LAUNCH_SMTOPK(1);
+  else if (E <= 16) FR_LAUNCH_SMTOPK(2);
+  else if (E <= 32) FR_LAUNCH_SMTOPK(4);
+  else if (E <= 64) FR_LAUNCH_SMTOPK(8);
+  else if (E <= 128) FR_LAUNCH_SMTOPK(16);
+  else FR_LAUNCH_SMTOPK(32);
+#undef FR_LAUNCH_SMTOPK
+  return static_cast<int>(cudaGetLastError());
+}
+
+int softmax_topk_dispatch(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e,
+                          int k, int renormalize, float* weights, int64_t w_stride, int32_t* ids,
+                          int64_t id_stride, int32_t* source_rows, int64_t src_stride, cudaStream_t st) {
+  if (!logits || !weights || !ids || M < 0 || E <= 0 || k <= 0 || k > E) return FR_ERR_ARG;
+  if (E > 256 || k > KMAX || static_cast<int64_t>(k) * M > 0x7fffffffLL) return FR_ERR_UNSUPPORTED;
+  if (M == 0) return FR_OK;
+  switch (dtype) {
+    case FR_F16:
+      return launch_softmax_topk<__half>(logits, M, E, stride_m, stride_e, k, renormalize, weights, w_stride, ids,
+                                         id_stride, source_rows, src_stride, st);
+    case FR_BF16:
+      return launch_softmax_topk<__nv_bfloat16>(logits, M, E, stride_m, stride_e, k, renormalize, weights,
+                                                w_stride, ids, id_stride, source_rows, src_stride, st);
+    case FR_F32:
+      return launch_softmax_topk<float>(logits, M, E, stride_m, stride_e, k, renormalize, weights, w_stride, ids,
+                                        id_stride, source_rows, src_stride, st);
+    default:
+      return FR_ERR_ARG;
+  }
+}
+
+// ----------------------------------------------------------------------------------
 // align: one thread-block cluster (1..8 CTAs) sorts all n ids.  Warp g of the cluster owns
 // the contiguous slice [g*seg, (g+1)*seg) of the flat ids, so (cta, warp, row-of-32, lane)
 // order is flat-index order and the sort is stable by construction.

@@ -59,6 +59,16 @@ int fr_topk_softmax(const void* logits, int dtype, int64_t M, int E, int64_t str
                     int topk, int renormalize, float* weights, int64_t w_stride, int32_t* ids,
                     int64_t id_stride, int fill_rest, void* stream);
 
+/* Softmax over all E columns followed by top-k on the probabilities (ties -> lower expert id):
+ * the routing of the reference's baseline layer, fast_route/fast_route/layers/vllm_route.py:72-84,
+ * i.e. vllm._moe_C.topk_softmax of vLLM 0.4.0 plus the optional renormalisation at :83-84.
+ * weights fp32 / ids int32 / source_rows int32 (may be NULL; entry [t,j] = j*M + t, the op's
+ * token_expert_indicies) are written at [row*stride + j].  renormalize != 0 divides the k
+ * probabilities by their sum.  Limits: E <= 256, topk <= 8, else FR_ERR_UNSUPPORTED. */
+int fr_softmax_topk(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e,
+                    int topk, int renormalize, float* weights, int64_t w_stride, int32_t* ids,
+                    int64_t id_stride, int32_t* source_rows, int64_t src_stride, void* stream);
+
 /* Stable counting sort of the n = M*topk flattened routing ids by expert, every expert's
  * segment padded to a multiple of block_size with the sentinel n.  Stands in for
  * moe_align_block_size, fast_route/fast_route/ops/fused_moe.py:133-175 (the vLLM 0.4.0 CUDA

@@ -20,15 +20,20 @@ Pinning status (what each restatement has been checked against):
   only known answer the reference carries is the docstring example at
   ``fast_route/fast_route/ops/fused_moe.py:151-159``; the restatement reproduces
   it.  Beyond that example: PARITY UNPINNED (no reference test covers it).
+* softmax-then-top-k routing of the baseline layer (``softmax_topk``): the op is
+  ``vllm._moe_C.topk_softmax`` of vLLM 0.4.0.post1, not part of the reference
+  tree.  Order rule and source-row formula restate that op's published kernel; the
+  weights are only held to the reference's tolerance for it
+  (``fast_route/tests/test_route.py:136-143``).  PARITY UNPINNED.
 """
 
 from .route import (exp_recipe, stable_topk, topk_softmax, route_from_hidden,
-                    full_argsort_fill)
+                    full_argsort_fill, softmax_topk)
 from .align import moe_align_block_size
 from .moe import silu_and_mul, torch_moe, moe_layer
 
 __all__ = [
     "exp_recipe", "stable_topk", "topk_softmax", "route_from_hidden",
-    "full_argsort_fill", "moe_align_block_size", "silu_and_mul", "torch_moe",
+    "full_argsort_fill", "softmax_topk", "moe_align_block_size", "silu_and_mul", "torch_moe",
     "moe_layer",
 ]

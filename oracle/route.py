@@ -100,6 +100,49 @@ def topk_softmax(logits, k: int, renormalize: bool = True):
     return w, ids
 
 
+def softmax_topk(logits, k: int, renormalize: bool = False):
+    """Softmax over all E columns, then top-k on the probabilities: the routing of the
+    reference's baseline layer (``fast_route/fast_route/layers/vllm_route.py:72-84``).
+
+    The op it calls, ``vllm._moe_C.topk_softmax``, belongs to vLLM 0.4.0.post1
+    (``requirements.txt:1``; not vendored): fp32 softmax, then k rounds of arg-max in which
+    equal probabilities go to the lower expert id, ``token_expert_indicies[t,j] = j*M + t``.
+    Parity of the weights is unpinned beyond the reference's own tolerance for this op
+    (``tests/test_route.py:136-143``, atol 1e-2); the bit recipe below is this build's:
+    e = exp_recipe(l - max), s = sums of 8 consecutive columns in ascending order combined by
+    a balanced binary tree over adjacent blocks (E padded with zeros to a power of two >= 8),
+    p = e * (1/s); renormalize: w_j = p_j / ((p_0 + p_1) + ...).
+
+    Returns (weights fp32 [M,k], ids int32 [M,k], source_rows int32 [M,k]).
+    """
+    l = _as_f32(logits)
+    M, E = l.shape
+    Ep = 8
+    while Ep < E:
+        Ep *= 2
+    mx = l.max(axis=1, keepdims=True)
+    e = np.zeros((M, Ep), dtype=_F)
+    e[:, :E] = exp_recipe((l - mx).astype(_F))
+    blocks = e.reshape(M, Ep // 8, 8)
+    part = blocks[:, :, 0].copy()
+    for i in range(1, 8):
+        part = (part + blocks[:, :, i]).astype(_F)
+    while part.shape[1] > 1:
+        part = (part[:, 0::2] + part[:, 1::2]).astype(_F)
+    inv = (_F(1.0) / part[:, 0]).astype(_F)
+    p = (e[:, :E] * inv[:, None]).astype(_F)
+    order = np.argsort(-p, axis=1, kind="stable")[:, :k]
+    ids = order.astype(np.int32)
+    w = np.take_along_axis(p, order, axis=1)
+    if renormalize:
+        s = w[:, 0].copy()
+        for j in range(1, k):
+            s = (s + w[:, j]).astype(_F)
+        w = (w / s[:, None]).astype(_F)
+    src = (np.arange(k, dtype=np.int64)[None, :] * M + np.arange(M, dtype=np.int64)[:, None]).astype(np.int32)
+    return w, ids, src
+
+
 def full_argsort_fill(logits, k: int):
     """What the reference leaves in caller-provided ``[M,E]`` buffers.
 

@@ -333,3 +333,26 @@ def test_fine_grained_skewed_full_size(dev):
     diff = (out[rows].float() - ref).abs()
     assert (diff <= MAX_ABS + ref.abs() * 2.0 ** -7).all()
     assert (diff.mean() / ref.abs().mean()).item() <= MEAN_REL
+
+
+@pytest.mark.parametrize("M,H,I,E,k,dt,renorm", [(300, 512, 384, 8, 2, torch.bfloat16, True),
+                                                 (300, 512, 384, 8, 2, torch.bfloat16, False),
+                                                 (1000, 256, 640, 64, 6, torch.float16, True),
+                                                 (1, 512, 1024, 8, 2, torch.bfloat16, True)])
+def test_baseline_layer_with_softmax_then_topk_routing(dev, M, H, I, E, k, dt, renorm):
+    """Same signature and semantics as the reference's baseline layer
+    (fast_route/fast_route/layers/vllm_route.py:17-110): logits rounded to the input dtype, fp32
+    softmax over all experts, top-k on the probabilities, optional renormalisation."""
+    from fast_route_b200.layers import vllm_route
+    x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=4, dtype=dt, weight_std=0.05)
+    xd, gd = x.to(dev), gate.to(dev)
+    out = vllm_route.fused_moe(xd, gd, w1.to(dev), w2.to(dev), k, renormalize=renorm)
+    _, _, logits = fr.fused_route(xd, gd, k, return_logits=True)
+    rounded = logits.to(dt).cpu()                                  # what `hidden_states @ gate` returns
+    ow, oi, _ = oracle.softmax_topk(rounded, k, renormalize=renorm)
+    ref, _, _ = oracle.moe_layer(x, gate, w1, w2, k, routing=(ow, oi))
+    check_layer(out, ref)
+    # routing from CPU fp32 logits agrees except on near ties of the rounded logits
+    cpu_logits = (x.float() @ gate.float()).to(dt)
+    _, ci, _ = oracle.softmax_topk(cpu_logits, k, renormalize=renorm)
+    assert (ci == oi).all(1).mean() > 0.97

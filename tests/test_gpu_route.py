@@ -186,3 +186,46 @@ def test_route_align_fused_entry_point(dev, E, k, M, dt, with_ws):
     assert np.array_equal(ids, oi) and np.array_equal(bits(w), bits(ow))
     assert npost == int(on[0]) and np.array_equal(s, os_)
     assert np.array_equal(e[:npost // bs], oe[:npost // bs]) and (e[npost // bs:] == -1).all()
+
+
+@pytest.mark.parametrize("E,k", [(1, 1), (4, 2), (8, 2), (16, 4), (60, 6), (64, 6), (100, 3), (128, 8), (256, 8)])
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16, torch.float32])
+def test_softmax_then_topk_baseline_routing(dev, E, k, dt):
+    """Routing of the reference's baseline layer (fast_route/fast_route/layers/vllm_route.py:72-84):
+    bit-exact against the oracle recipe, with and without renormalisation, ties included."""
+    from fast_route_b200.ops.vllm_route import topk_softmax
+    for M in (1, 37, 4096):
+        logits = synth.routing_logits(M, E, k, seed=E + k, dtype=dt, dup_frac=0.3)
+        lg = logits.to(dev)
+        for renorm in (False, True):
+            w = torch.empty(M, k, dtype=torch.float32, device=dev)
+            ids = torch.empty(M, k, dtype=torch.int32, device=dev)
+            src = torch.empty(M, k, dtype=torch.int32, device=dev)
+            topk_softmax(w, ids, src, lg, renormalize=renorm)
+            ow, oi, osrc = oracle.softmax_topk(logits, k, renormalize=renorm)
+            assert np.array_equal(ids.cpu().numpy(), oi), (E, k, M, renorm)
+            assert np.array_equal(bits(w.cpu().numpy()), bits(ow)), (E, k, M, renorm)
+            assert np.array_equal(src.cpu().numpy(), osrc)
+        if M > 1:
+            # the reference's tolerance for this op (tests/test_route.py:136-143) against library softmax
+            p = torch.softmax(logits.float(), -1)
+            ref = torch.gather(p, 1, torch.from_numpy(oi.astype(np.int64)))
+            w = torch.empty(M, k, dtype=torch.float32, device=dev)
+            ids = torch.empty(M, k, dtype=torch.int32, device=dev)
+            topk_softmax(w, ids, None, lg)
+            assert (w.cpu() - ref).abs().max() < 1e-6
+
+
+def test_softmax_then_topk_strided_and_limits(dev):
+    from fast_route_b200 import _lib
+    from fast_route_b200.ops.vllm_route import topk_softmax
+    base = synth.routing_logits(300, 128, 4, seed=9, dtype=torch.float32)
+    view = base.to(dev)[:, ::2]                                 # element stride 2
+    w = torch.empty(300, 4, dtype=torch.float32, device=dev)
+    ids = torch.empty(300, 4, dtype=torch.int32, device=dev)
+    topk_softmax(w, ids, None, view)
+    ow, oi, _ = oracle.softmax_topk(base[:, ::2], 4)
+    assert np.array_equal(ids.cpu().numpy(), oi) and np.array_equal(bits(w.cpu().numpy()), bits(ow))
+    big = torch.zeros(4, 512, device=dev)
+    with pytest.raises(_lib.FastRouteError):
+        topk_softmax(torch.empty(4, 2, device=dev), torch.empty(4, 2, dtype=torch.int32, device=dev), None, big)

@@ -102,3 +102,27 @@ def test_exp_recipe_accuracy_and_tie_rule():
     assert full.tolist() == [[1, 2, 4, 0, 3, 5, 6, 7]]   # -0.0 and +0.0 tie -> lower id first
     wt = torch.softmax(torch.sort(torch.from_numpy(logits), descending=True, stable=True)[0][:, :4], -1)
     np.testing.assert_allclose(w, wt.numpy(), atol=1e-6)
+
+
+def test_softmax_topk_order_rule_and_source_rows():
+    """Baseline-layer routing (softmax over all experts, then top-k): equal probabilities go to the
+    lower expert id, weights are the plain softmax, source rows are j*M + t
+    (fast_route/fast_route/layers/vllm_route.py:72-84 and the vLLM 0.4.0 op it calls)."""
+    rng = np.random.default_rng(5)
+    for E, k in ((8, 2), (60, 6), (64, 6), (128, 8), (256, 4)):
+        logits = rng.standard_normal((257, E)).astype(np.float32)
+        logits[::5, 1] = logits[::5, 0]                       # exact ties
+        logits[::7] = 0.25                                    # all-equal rows
+        w, ids, src = oracle.softmax_topk(logits, k)
+        p64 = torch.softmax(torch.from_numpy(logits).double(), -1).numpy()
+        assert np.abs(w - np.take_along_axis(p64, ids.astype(np.int64), 1)).max() < 2e-7
+        assert np.array_equal(ids[::7], np.tile(np.arange(k, dtype=np.int32), (len(ids[::7]), 1)))
+        # selection is a valid stable top-k of the probabilities
+        order = np.argsort(-p64, axis=1, kind="stable")[:, :k]
+        agree = (order == ids).all(1)
+        assert agree.mean() > 0.99          # fp32 vs fp64 may order near-equal probabilities differently
+        assert np.array_equal(src, np.arange(k)[None, :] * 257 + np.arange(257)[:, None])
+        wr, ids2, _ = oracle.softmax_topk(logits, k, renormalize=True)
+        assert np.array_equal(ids, ids2)
+        assert np.abs(wr.sum(1) - 1).max() < 1e-6
+        assert np.abs(wr - w / w.sum(1, keepdims=True)).max() < 2e-7
