@@ -54,6 +54,8 @@ SIGNATURES = {
     "fr_moe_experts_peer": (_I, [_P, _L, _I, _L, _P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _L, _P, _P, _Z, _P]),
     "fr_combine_peer": (_I, [_P, _L, _I, _L, _I, _P, _P, _L, _I, _I, _P, _L, _P]),
     "fr_gather_rows": (_I, [_P, _L, _P, _L, _I, _P, _L, _P]),
+    "fr_w4a16_gemm": (_I, [_P, _L, _P, _P, _P, _L, _I, _I, _I, _P, _L, _I, _P]),
+    "fr_w4a16_dequant": (_I, [_P, _P, _P, _I, _I, _I, _P, _L, _P]),
 }
 
 _lib = None

@@ -4,4 +4,5 @@
 #include "fr_route_coop.cu"
 #include "fr_gemm.cu"
 #include "fr_gemm_tokenn.cu"
+#include "fr_w4a16.cu"
 #include "fr_api.cu"

@@ -706,6 +706,18 @@ int fr_topk_softmax(const void* logits, int dtype, int64_t M, int E, int64_t str
                                id_stride, fill_rest, static_cast<cudaStream_t>(stream));
 }
 
+int fr_w4a16_gemm(const void* a, int64_t lda, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                  int64_t m, int n, int k, int groupsize, void* c, int64_t ldc, int split_k, void* stream) {
+  return fr::w4a16_gemm_dispatch(a, lda, qweight, scales, qzeros, m, n, k, groupsize, c, ldc, split_k,
+                                 static_cast<cudaStream_t>(stream));
+}
+
+int fr_w4a16_dequant(const int32_t* qweight, const void* scales, const int32_t* qzeros, int n, int k, int groupsize,
+                     void* w, int64_t ldw, void* stream) {
+  return fr::w4a16_dequant_dispatch(qweight, scales, qzeros, n, k, groupsize, w, ldw,
+                                    static_cast<cudaStream_t>(stream));
+}
+
 int fr_softmax_topk(const void* logits, int dtype, int64_t M, int E, int64_t stride_m, int64_t stride_e, int topk,
                     int renormalize, float* weights, int64_t w_stride, int32_t* ids, int64_t id_stride,
                     int32_t* source_rows, int64_t src_stride, void* stream) {

@@ -255,6 +255,23 @@ int fr_combine_peer(const void* const* peer_y, int64_t ld_y, int world, int64_t 
 int fr_gather_rows(const void* src, int64_t ld_src, const int32_t* idx, int64_t rows, int row_bytes, void* dst,
                    int64_t ld_dst, void* stream);
 
+/* W4A16 small-batch GEMM with split-K: c[m,n] = a[m,k] . dequant(qweight)[k,n].  Stands in for
+ * matmul_split_k and its Triton kernel, benchmarks/splitk_gemm/splitk.py:26-103 and :178-216.
+ * a fp16 [m,k] (row pitch lda elements), qweight int32 [k/8, n] (nibble j of word [kk,n] is row
+ * 8*kk+j), scales fp16 [k/groupsize, n], qzeros int32 [k/groupsize, n/8] (nibble j of word [g,nn]
+ * is column 8*nn+j), all dense row-major; c fp16 [m,n] (row pitch ldc).
+ * w = fp16(q)*s - fp16(z+1)*s with every operation rounded to fp16 (:83-87); fp32 accumulation.
+ * The K slices are reduced in a fixed order inside one kernel (the reference adds them with fp16
+ * atomics, :103), so the result is deterministic.  split_k: 0 = choose, or 1, 2, 4, 8.
+ * Requirements: n % 8 == 0, k % 64 == 0, groupsize % 64 == 0, k % groupsize == 0, lda % 8 == 0. */
+int fr_w4a16_gemm(const void* a, int64_t lda, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                  int64_t m, int n, int k, int groupsize, void* c, int64_t ldc, int split_k, void* stream);
+
+/* The dense fp16 weight matrix w[k,n] (row pitch ldw) that fr_w4a16_gemm multiplies with, produced with
+ * the same arithmetic (benchmarks/splitk_gemm/splitk.py:83-87). */
+int fr_w4a16_dequant(const int32_t* qweight, const void* scales, const int32_t* qzeros, int n, int k,
+                     int groupsize, void* w, int64_t ldw, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

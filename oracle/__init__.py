@@ -20,6 +20,9 @@ Pinning status (what each restatement has been checked against):
   only known answer the reference carries is the docstring example at
   ``fast_route/fast_route/ops/fused_moe.py:151-159``; the restatement reproduces
   it.  Beyond that example: PARITY UNPINNED (no reference test covers it).
+* W4A16 split-K GEMM (``w4a16``): pinned against the reference's Triton kernel
+  (``benchmarks/splitk_gemm/splitk.py:26-103``) executed on CPU with
+  ``TRITON_INTERPRET=1``; vectors under ``tests/golden``.
 * softmax-then-top-k routing of the baseline layer (``softmax_topk``): the op is
   ``vllm._moe_C.topk_softmax`` of vLLM 0.4.0.post1, not part of the reference
   tree.  Order rule and source-row formula restate that op's published kernel; the
@@ -31,9 +34,10 @@ from .route import (exp_recipe, stable_topk, topk_softmax, route_from_hidden,
                     full_argsort_fill, softmax_topk)
 from .align import moe_align_block_size
 from .moe import silu_and_mul, torch_moe, moe_layer
+from . import w4a16
 
 __all__ = [
     "exp_recipe", "stable_topk", "topk_softmax", "route_from_hidden",
     "full_argsort_fill", "softmax_topk", "moe_align_block_size", "silu_and_mul", "torch_moe",
-    "moe_layer",
+    "moe_layer", "w4a16",
 ]

@@ -16,6 +16,11 @@ It executes, on the CPU:
     and activation (``benchmarks/swizzle_moe/activation.py:27-30``), extracted from
     the source text because the modules import an absent vLLM build.
 
+  * the reference's W4A16 split-K Triton kernel ``hint_kernel``
+    (``benchmarks/splitk_gemm/splitk.py:26-103``) launched with the tile sizes of its host
+    wrapper (``:183-190``; the wrapper itself is not called: it dumps compiler output next to
+    the source), on inputs drawn like its ``make_tensor`` (``:267-275``).
+
 Outputs are small ``.npz`` files.  The tests only read the ``.npz`` files; they
 never need the reference tree.
 """
@@ -159,8 +164,48 @@ def golden_layer():
     print("torch_moe.npz")
 
 
+def w4a16_inputs(m, k, n, groupsize, seed):
+    """Seeded inputs distributed like the reference's make_tensor (normal std 0.5 / uniform int32)."""
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    a = (torch.randn(m, k, generator=g) * 0.5).half()
+    b = torch.randint(-2**31, 2**31 - 1, (k // 8, n), generator=g, dtype=torch.int64).to(torch.int32)
+    zeros = torch.randint(-2**31, 2**31 - 1, (k // groupsize, n // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    scales = (torch.randn(k // groupsize, n, generator=g) * 0.5).half()
+    return a, b, scales, zeros
+
+
+def golden_w4a16():
+    sys.path.insert(0, os.path.join(REF, "benchmarks", "splitk_gemm"))
+    import splitk as ref_splitk
+    out = {}
+    # case 2 has one-hot activation rows, so its output rows are single dequantised weight rows, exactly
+    cases = [(16, 512, 64), (32, 1024, 96), (64, 512, 64)]
+    for ci, (m, k, n) in enumerate(cases):
+        groupsize, block_m, block_n, block_k, group_m, split_k = 128, 16, 32, 128, 8, 4
+        a, b, scales, zeros = w4a16_inputs(m, k, n, groupsize, 40 + ci)
+        if ci == 2:
+            rows = (torch.arange(m) * 8 + torch.arange(m) % 8) % k      # every nibble position, every group
+            a = torch.zeros(m, k, dtype=torch.float16)
+            a[torch.arange(m), rows] = 1.0
+            out["onehot_rows"] = rows.numpy()
+        c = torch.zeros((m, n), dtype=torch.float16)
+        grid = (triton.cdiv(m, block_m) * triton.cdiv(n, block_n), split_k)
+        ref_splitk.hint_kernel[grid](a, b, c, scales, zeros,
+                                     a.stride(0), a.stride(1), b.stride(0), b.stride(1), c.stride(0), c.stride(1),
+                                     scales.stride(0), scales.stride(1), zeros.stride(0), zeros.stride(1),
+                                     groupsize, m, n, k, block_m, block_n, block_k, group_m, split_k)
+        out[f"a_{ci}"] = a.numpy()
+        out[f"b_{ci}"] = b.numpy()
+        out[f"scales_{ci}"] = scales.numpy()
+        out[f"zeros_{ci}"] = zeros.numpy()
+        out[f"c_{ci}"] = c.numpy()
+    np.savez_compressed(os.path.join(HERE, "w4a16.npz"), **out)
+    print("w4a16.npz", len(cases), "cases")
+
+
 if __name__ == "__main__":
     torch.set_num_threads(8)
     golden_argsort()
     golden_route()
     golden_layer()
+    golden_w4a16()

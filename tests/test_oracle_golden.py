@@ -126,3 +126,30 @@ def test_softmax_topk_order_rule_and_source_rows():
         assert np.array_equal(ids, ids2)
         assert np.abs(wr.sum(1) - 1).max() < 1e-6
         assert np.abs(wr - w / w.sum(1, keepdims=True)).max() < 2e-7
+
+
+def test_w4a16_oracle_matches_reference_kernel():
+    """Outputs of the reference's W4A16 split-K Triton kernel (benchmarks/splitk_gemm/splitk.py:26-103)
+    run on CPU.  One-hot activations make output rows equal single dequantised weight rows, which pins
+    the fp16 dequantisation bit for bit; the random cases agree to the fp16 roundings of the reference's
+    four atomically added K slices."""
+    g = np.load(os.path.join(GOLD, "w4a16.npz"))
+    w = oracle.w4a16.dequant(g["b_2"], g["scales_2"], g["zeros_2"])
+    assert np.array_equal(w[g["onehot_rows"]].view(np.uint16), g["c_2"].view(np.uint16))
+    for ci in range(2):
+        ref = oracle.w4a16.matmul_split_k(g[f"a_{ci}"], g[f"b_{ci}"], g[f"scales_{ci}"], g[f"zeros_{ci}"])
+        c = g[f"c_{ci}"].astype(np.float64)
+        # 4 partial sums each rounded to fp16 (2^-11 relative) plus the roundings of the running sum
+        assert (np.abs(c - ref) <= 8 * 2.0 ** -11 * np.maximum(np.abs(ref), 64.0)).all()
+
+
+def test_w4a16_dequant_known_answers():
+    """Hand-computed nibble order: word 0x76543210 holds q = 0..7 for rows k = 0..7 (:62, :70, :86);
+    zero-point word 0x00000021 gives z = 1 for column 0 and z = 2 for column 1 (:65, :71, :83)."""
+    b = np.full((8, 8), 0x76543210, dtype=np.int64).astype(np.int32)          # k = 64
+    scales = np.full((1, 8), 0.5, dtype=np.float16)
+    zeros = np.array([[0x00000021]], dtype=np.int32)
+    w = oracle.w4a16.dequant(b, scales, zeros, groupsize=64).astype(np.float64)
+    q = np.tile(np.arange(8), 8)
+    z = np.array([1, 2, 0, 0, 0, 0, 0, 0])
+    assert np.array_equal(w, (q[:, None] - (z[None, :] + 1)) * 0.5)
