@@ -327,6 +327,54 @@ def routing_latency(fr, synth, dev):
     return out
 
 
+def w4a16_splitk(dev, peaks):
+    """The reference's W4A16 split-K GEMM (benchmarks/splitk_gemm/splitk.py: m=16, k=n=4096, group 128) and
+    neighbours in m.  HBM-bound on the packed weights; 20 weight sets (173 MB > L2) are cycled inside one CUDA
+    graph so every launch streams its weights from DRAM.  The dense fp16 matmul of the framework on the
+    dequantised matrix is timed beside it for scale."""
+    from fast_route_b200.ops import splitk_gemm as sk
+    gs = 128
+    g = torch.Generator(device=dev).manual_seed(3)
+    rows = []
+    # the reference's driver shape, and a large FFN-sized matrix (117 MB packed) where the kernel is in steady state
+    for k, n, sets, ms in ((4096, 4096, 20, (1, 16, 64, 256)), (8192, 28672, 2, (16,))):
+        bs = [torch.randint(-2**31, 2**31 - 1, (k // 8, n), generator=g, device=dev, dtype=torch.int64).to(torch.int32)
+              for _ in range(sets)]
+        zs = [torch.randint(-2**31, 2**31 - 1, (k // gs, n // 8), generator=g, device=dev, dtype=torch.int64)
+              .to(torch.int32) for _ in range(sets)]
+        ss = [(torch.randn(k // gs, n, generator=g, device=dev) * 0.5).half() for _ in range(sets)]
+        dense = [sk.dequantize(bs[i], ss[i], zs[i], gs) for i in range(sets)]
+        for m in ms:
+            a = (torch.randn(m, k, generator=g, device=dev) * 0.5).half()
+            c = torch.empty(m, n, dtype=torch.float16, device=dev)
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for i in range(sets):
+                    sk.matmul_split_k(a, bs[i], ss[i], zs[i], gs, out=c)
+            us = cuda_time_ms(gr.replay, 20, 3)[0] * 1e3 / sets
+            torch.matmul(a, dense[0], out=c)          # library handle and workspace exist before the capture
+            torch.cuda.synchronize()
+            gd = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gd):
+                for i in range(sets):
+                    torch.matmul(a, dense[i], out=c)
+            us_dense = cuda_time_ms(gd.replay, 20, 3)[0] * 1e3 / sets
+            gl = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gl):
+                for i in range(sets):
+                    sk.matmul_split_k(a, bs[0], ss[0], zs[0], gs, out=c)
+            us_l2 = cuda_time_ms(gl.replay, 20, 3)[0] * 1e3 / sets
+            del gr, gd, gl
+            nbytes = k * n // 2 + (k // gs) * n * 2 + (k // gs) * (n // 8) * 4 + m * k * 2 + m * n * 2
+            rows.append({"m": m, "k": k, "n": n, "groupsize": gs, "us": round(us, 3),
+                         "us_same_weights_every_launch": round(us_l2, 3),
+                         "us_dense_fp16_framework_matmul": round(us_dense, 3), "algorithmic_bytes": nbytes,
+                         "hbm_gbs": nbytes / us / 1e3, "frac_hbm_peak": nbytes / us / 1e3 / peaks["hbm_gbs"],
+                         "tflops": 2.0 * m * n * k / us / 1e6})
+        del bs, zs, ss, dense
+    return rows
+
+
 def gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps):
     """Times the dominant kernel (grouped GEMM 1 + SiLU*mul epilogue) alone through the C ABI."""
     from fast_route_b200.ops import fused_moe as fm
@@ -362,6 +410,9 @@ def run_ours(args, rank, world, local_rank):
 
     if args.routing_only:
         print(json.dumps({"routing_latency": routing_latency(fr, synth, dev)}), flush=True)
+        return
+    if args.w4a16_only:
+        print(json.dumps({"w4a16_splitk_gemm": w4a16_splitk(dev, peaks)}), flush=True)
         return
 
     if world > 1:
@@ -502,6 +553,7 @@ def run_ours(args, rank, world, local_rank):
             line["routing_latency"] = routing_latency(fr, synth, dev)
             line["transformer_block"] = transformer_block(fr, wg, w1, w2, M, H, k)
             line["fp8_weights_mode"] = fp8_points(fr, synth, wg, w1, w2, H, I, E, k, peaks)
+            line["w4a16_splitk_gemm"] = w4a16_splitk(dev, peaks)
         if not args.no_cpu:
             cb = cpu_reference_rate(H, I, E, k, args.cpu_tokens, 3, warm=1, weights=(wg, w1, w2), budget_s=20.0)
             line["cpu_baseline"] = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
@@ -529,6 +581,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--routing-only", action="store_true",
                     help="only the routing/align latency microbenchmark (16384 tokens, E in 8/64/128)")
+    ap.add_argument("--w4a16-only", action="store_true",
+                    help="only the W4A16 split-K GEMM microbenchmark (k = n = 4096, group 128, m in 1/16/64/256)")
     ap.add_argument("--profile", action="store_true",
                     help="only warm-up + timed layer steps (for ncu captures): no e2e, sweep, roofline or CPU legs")
     args = ap.parse_args()

@@ -5,13 +5,20 @@
 //   qzeros[k/g, n/8] int32, nibble j of word [gi, nn] belongs to column n = 8*nn + j;
 //   w[k,n] = fp16(q) * s  -  fp16(z + 1) * s,  every operation rounded to fp16 (:83-87).
 //
-// B200 mapping.  The layer is bound by streaming the packed weights once, so weights sit on the MMA M axis
-// (128 output columns per CTA) and the few activation rows on the MMA N axis (16..256):
-//   warp 0    TMA producer: per 64-wide K step the packed tile (8 words x 128 columns, 4 KB) and the activation
-//             tile (m_pad rows x 64, 128-byte swizzle) into a ring of input stages
-//   warps 4-7 dequantise: thread t owns output column n0+t, expands 8 packed words into eight 16-byte rows of the
-//             K-major, 128-byte-swizzled operand tile in shared memory, then drain the accumulator at the end
-//   warp 1    one thread issues tcgen05.mma (M=128, N=m_pad, fp32 accumulator in TMEM)
+// B200 mapping.  The packed weights are streamed once, so weights sit on the MMA M axis (128 output columns per
+// CTA) and the few activation rows on the MMA N axis (16..128 per launch); a K step is 64 wide.
+// The K steps of a CTA are dealt round-robin to four independent pipelines ("groups"), each with its own input
+// stages, two operand tiles, an fp32 accumulator in TMEM and its own barriers:
+//   warp p (p = 0..3), one thread: TMA producer and MMA issuer of group p.  Loads the packed tile (8 words x 128
+//              columns, 4 KB) and the activation tile (m_pad rows x 64, 128-byte swizzle) of the group's steps, and
+//              issues tcgen05.mma (M=128, N=m_pad) on every operand tile the dequantisers hand over.
+//   warps 4+4p .. 7+4p: the 128 dequantisers of group p.  Thread t owns output column n0+t and expands the 8 packed
+//              words of a step into the 128-byte row t of a K-major, 128-byte-swizzled operand tile.
+// With so few activation rows an MMA is all issue latency (about 500 cycles for the four of a step), so one issuing
+// thread per CTA was the bottleneck; four pipelines that never wait for one another hide it.  The dequantising
+// warps drain the four accumulators at the end; warp 1 also allocates and frees TMEM.
+// The dequantisation is bound by instruction issue (about 2.5 instructions per weight for the exact fp16 recipe),
+// not by HBM.
 // Split-K runs as a thread-block cluster along K (1, 2, 4 or 8 CTAs): every CTA parks its fp32 partial tile in its
 // own shared memory, and after a cluster barrier CTA r sums rows r, r+S, ... over the ranks in rank order through
 // distributed shared memory.  No workspace, no atomics: the result does not depend on timing (the reference
@@ -26,11 +33,16 @@ namespace cgx = cooperative_groups;
 
 constexpr int W4_BN = 128;                 // output columns (weight rows of the MMA) per CTA
 constexpr int W4_BK = 64;                  // K step: one 128-byte operand row
-constexpr int W4_WSTAGES = 3;              // dequantised operand ring
+constexpr int W4_GROUPS = 4;               // dequantising groups of 128 threads, each with its own accumulator
+constexpr int W4_WBUFS = 2;                // dequantised operand tiles per group
+constexpr int W4_WSTAGES = W4_GROUPS * W4_WBUFS;
 constexpr int W4_W_BYTES = W4_BN * W4_BK * 2;   // 16 KB
 constexpr int W4_RAW_BYTES = 8 * W4_BN * 4;     // 4 KB of packed words
-constexpr int W4_MAX_IN = 8;               // input ring depth (packed tile + activation tile)
-constexpr int W4_SMEM_BUDGET = 200 * 1024;
+constexpr int W4_MAX_IN = 16;              // input ring depth (packed tile + activation tile)
+constexpr int W4_SMEM_BUDGET = 224 * 1024;
+constexpr int W4_MAX_M = 128;              // activation rows per launch (MMA N); larger batches run in chunks
+constexpr int W4_THREADS = 128 + W4_GROUPS * 128;
+
 
 struct W4Params {
   const __half* scales;    // [k/g, n]
@@ -38,35 +50,67 @@ struct W4Params {
   __half* c;
   int64_t ldc;
   int m;                   // valid activation rows of this launch (<= m_pad)
-  int m_pad;               // MMA N: multiple of 16, <= 256
+  int m_pad;               // MMA N: multiple of 16, <= 128
   int n, k;
-  int groupsize;           // multiple of 64
+  int groupsize;           // multiple of 64 (a K step never straddles two groups)
   int in_stages;
   int x_bytes;             // m_pad * 128
   uint32_t tmem_cols;
 };
 
-// eight fp16 weights of one packed word: w_j = q_j * s - zs, each operation rounded to fp16 (no fused multiply-add)
-__device__ __forceinline__ uint4 w4_dequant8(uint32_t v, __half2 s2, __half2 zs2) {
-  const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
-  uint32_t out[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    // nibbles 2i (low half) and 2i+1 (high half) as 1024 + q in fp16, which is exact
-    const uint32_t lo = (v >> (8 * i)) & 0xFu, hi = (v >> (8 * i + 4)) & 0xFu;
-    const uint32_t bits = 0x64006400u | lo | (hi << 16);
-    __half2 q = __hsub2_rn(*reinterpret_cast<const __half2*>(&bits), k1024);
-    q = __hsub2_rn(__hmul2_rn(q, s2), zs2);
-    out[i] = *reinterpret_cast<uint32_t*>(&q);
+// Scale-dependent constants of one (column, group) and the expansion of one packed word into eight fp16 weights
+// w_j = q_j * s - zs, both operations rounded to fp16 and not fused with each other.
+//
+// Fast path (2^-9 <= |s| < 32).  Byte i of the word holds nibbles 2i and 2i+1.  Replicating the byte into both
+// halves and masking with 0x00F0000F | 0x64006400 gives the fp16 pair (1024 + q_2i, 1024 + 16 * q_2i+1), exactly.
+// One fused multiply-add per pair, fma(1024 + q, s, -1024 s) and fma(1024 + 16 q, s / 16, -64 s), evaluates
+// q * s exactly and rounds it once, which is what fp16(q) * s does: s / 16, 1024 s and 64 s are exact in this
+// range.  The pair comes out in memory order.
+// Slow path (any other scale, zero and subnormal-prone ones included): integer nibbles -> fp16 -> multiply.
+struct W4Group {
+  __half2 s2, zs2, mul2, add2;
+  bool fast;
+  __device__ __forceinline__ void set(__half s, uint32_t z) {
+    s2 = __half2half2(s);
+    zs2 = __half2half2(__hmul_rn(__ushort2half_rn(static_cast<unsigned short>(z + 1)), s));
+    const unsigned short mag = __half_as_ushort(s) & 0x7FFFu;
+    fast = mag >= 0x1800u && mag < 0x5000u;
+    const __half s16 = __hmul_rn(s, __ushort_as_half(0x2C00));          // s / 16
+    mul2 = __halves2half2(s, s16);
+    add2 = __halves2half2(__hneg(__hmul_rn(s, __ushort_as_half(0x6400))),      // -1024 s
+                          __hneg(__hmul_rn(s, __ushort_as_half(0x5400))));     // -64 s
   }
-  return make_uint4(out[0], out[1], out[2], out[3]);
-}
+  template <bool FAST>
+  __device__ __forceinline__ uint4 expand(uint32_t v) const {
+    uint32_t out[4];
+    if constexpr (FAST) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t bits = (__byte_perm(v, 0u, 0x4040u | (i << 8) | i) & 0x00F0000Fu) | 0x64006400u;
+        __half2 q = __hfma2(*reinterpret_cast<const __half2*>(&bits), mul2, add2);
+        q = __hsub2_rn(q, zs2);
+        out[i] = *reinterpret_cast<uint32_t*>(&q);
+      }
+    } else {
+      const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t bits = 0x64006400u | ((v >> (8 * i)) & 0xFu) | (((v >> (8 * i + 4)) & 0xFu) << 16);
+        __half2 q = __hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&bits), k1024), s2);
+        q = __hsub2_rn(q, zs2);
+        out[i] = *reinterpret_cast<uint32_t*>(&q);
+      }
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+  }
+  __device__ __forceinline__ uint4 expand_any(uint32_t v) const { return fast ? expand<true>(v) : expand<false>(v); }
+};
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(W4_THREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // layout: [W ring][X ring][packed ring][barriers]; the W ring doubles as the fp32 partial tile at the end
+  // layout: [W ring][X ring][packed ring][barriers]; the front of it doubles as the fp32 partial tile at the end
   uint8_t* sW = smem;
   uint8_t* sX = sW + W4_WSTAGES * W4_W_BYTES;
   uint8_t* sQ = sX + p.in_stages * p.x_bytes;
@@ -77,7 +121,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* tfull = w_empty + W4_WSTAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-
   cgx::cluster_group cluster = cgx::this_cluster();
   const int S = static_cast<int>(cluster.num_blocks());
   const int rank = static_cast<int>(cluster.block_rank());
@@ -90,6 +133,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   const int kb_begin = min(KB, rank * per);
   const int kb_end = min(KB, kb_begin + per);
   const int nkb = kb_end - kb_begin;
+  const int in_stages = p.in_stages;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < W4_MAX_IN; ++s) {
@@ -97,10 +141,10 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(&in_empty[s], 1);
     }
     for (int s = 0; s < W4_WSTAGES; ++s) {
-      mbar_init(&w_full[s], 4);
+      mbar_init(&w_full[s], 4);      // the four warps of the owning group
       mbar_init(&w_empty[s], 1);
     }
-    mbar_init(tfull, 1);
+    mbar_init(tfull, W4_GROUPS);     // one arrival per group, after its last MMA
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmQ);
@@ -115,111 +159,155 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t in_stages = static_cast<uint32_t>(p.in_stages);
 
-  if (warp == 0) {
-    // ---------------- TMA producer ----------------
+  // Step i of the CTA belongs to group i % 4; its input stage is i % in_stages.  in_stages is a multiple of four, so
+  // a group always meets the same stages: own step j (i = grp + 4 j) uses stage grp + 4 * (j % spg).
+  const int spg = in_stages / W4_GROUPS;           // input stages per group
+
+  if (warp < W4_GROUPS) {
+    // ---------------- per group: TMA producer + MMA issuer (one thread) ----------------
     if (lane == 0) {
-      PipeState ps;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        // a stage is free once the MMAs that read its activation tile are complete; they were issued after the
-        // dequantisers had consumed its packed tile
-        if (!wait_or_abort(&in_empty[ps.stage], ps.phase ^ 1, abort_flag, 0x800)) break;
-        mbar_expect_tx(&in_full[ps.stage], W4_RAW_BYTES + p.x_bytes);
-        // the packed matrix is addressed as 16-bit elements: column 2*n, row k/8
-        tma_load_2d(sQ + ps.stage * W4_RAW_BYTES, &tmQ, &in_full[ps.stage], 2 * n0, kb * (W4_BK / 8));
-        tma_load_2d(sX + ps.stage * p.x_bytes, &tmX, &in_full[ps.stage], kb * W4_BK, 0);
-        ps.advance_rt(in_stages);
-      }
-    }
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
-    if (lane == 0) {
+      const int grp_id = warp;
+      const int own = nkb > grp_id ? (nkb - grp_id + W4_GROUPS - 1) / W4_GROUPS : 0;   // steps of this group
+      uint64_t* my_w_full = w_full + grp_id * W4_WBUFS;
+      uint64_t* my_w_empty = w_empty + grp_id * W4_WBUFS;
       const uint32_t idesc = umma_idesc_f16(false, W4_BN, p.m_pad);
-      PipeState pin, pw;
+      const uint32_t d_tmem = tmem_base + grp_id * p.m_pad;       // the group's own accumulator
+      auto load = [&](int j) {           // own step j -> its stage (the caller has made sure the stage is free)
+        const int st = grp_id + W4_GROUPS * (j % spg);
+        const int kb = kb_begin + grp_id + W4_GROUPS * j;
+        mbar_expect_tx(&in_full[st], W4_RAW_BYTES + p.x_bytes);
+        // the packed matrix is addressed as 16-bit elements: column 2*n, row k/8
+        tma_load_2d(sQ + st * W4_RAW_BYTES, &tmQ, &in_full[st], 2 * n0, kb * (W4_BK / 8));
+        tma_load_2d(sX + st * p.x_bytes, &tmX, &in_full[st], kb * W4_BK, 0);
+      };
+      const int pre = own < spg ? own : spg;
+      for (int j = 0; j < pre; ++j) load(j);
       bool ok = true;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
-        if (!wait_or_abort(&in_full[pin.stage], pin.phase, abort_flag, 0x810) ||
-            !wait_or_abort(&w_full[pw.stage], pw.phase, abort_flag, 0x811)) {
+      for (int j = 0; j < own && ok; ++j) {
+        // refill the stage of the previous own step first (its MMAs were issued a whole step ago)
+        if (j >= 1 && j - 1 + spg < own) {
+          const int pst = grp_id + W4_GROUPS * ((j - 1) % spg);
+          if (!wait_or_abort(&in_empty[pst], static_cast<uint32_t>((j - 1) / spg) & 1u, abort_flag, 0x800)) {
+            ok = false;
+            break;
+          }
+          load(j - 1 + spg);
+        }
+        const int buf = j % W4_WBUFS;
+        const int st = grp_id + W4_GROUPS * (j % spg);
+        // the dequantisers waited for this step's input stage before they wrote the operand tile
+        if (!wait_or_abort(&my_w_full[buf], static_cast<uint32_t>(j / W4_WBUFS) & 1u, abort_flag, 0x811)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint64_t adesc = umma_desc_sw128(smem_u32(sW + pw.stage * W4_W_BYTES));
-        const uint64_t bdesc = umma_desc_sw128(smem_u32(sX + pin.stage * p.x_bytes));
+        const uint64_t adesc = umma_desc_sw128(smem_u32(sW + (grp_id * W4_WBUFS + buf) * W4_W_BYTES));
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(sX + st * p.x_bytes));
 #pragma unroll
         for (int kk = 0; kk < W4_BK / 16; ++kk)
-          tc_mma_f16(tmem_base, adesc + 2 * kk, bdesc + 2 * kk, idesc, (kb > kb_begin || kk > 0) ? 1u : 0u);
-        tc_commit(&w_empty[pw.stage]);
-        tc_commit(&in_empty[pin.stage]);
-        pin.advance_rt(in_stages);
-        pw.advance<W4_WSTAGES>();
+          tc_mma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&my_w_empty[buf]);
+        tc_commit(&in_empty[st]);
       }
-      if (ok) tc_commit(tfull);
+      // all of the group's MMAs (none, for a group without steps) are complete when this arrives
+      if (ok && own > 0) tc_commit(tfull);
+      else mbar_arrive(tfull);
     }
-  } else if (warp >= 4) {
+  } else {
     // ---------------- dequantise, then drain ----------------
-    const int t = threadIdx.x - 128;            // 0..127: output column n0 + t, TMEM lane t
+    const int t = (threadIdx.x - 128) & 127;        // output column n0 + t, TMEM lane t
+    const int grp_id = (threadIdx.x - 128) >> 7;    // owns steps grp_id, grp_id + 4, ...
     const int n = n0 + t;
     const bool n_ok = n < p.n;
-    const int steps_per_group = p.groupsize / W4_BK;
     // byte offset of row t in a swizzled operand tile; the 16-byte chunk index is XORed with (t & 7)
     const uint32_t row_off = static_cast<uint32_t>(t >> 3) * 1024u + static_cast<uint32_t>(t & 7) * 128u;
-    PipeState pin, pw;
-    __half2 s2 = __half2half2(__ushort_as_half(0)), zs2 = s2;
-    int cur_group = -1;
+    uint8_t* w_base = sW + grp_id * (W4_WBUFS * W4_W_BYTES);
+    uint64_t* my_w_full = w_full + grp_id * W4_WBUFS;
+    uint64_t* my_w_empty = w_empty + grp_id * W4_WBUFS;
+    const __half* sp = p.scales + n;
+    const int32_t* zp = p.qzeros + (n >> 3);
+    const int zshift = (n & 7) * 4;
+    // scale and zero point of the group's next step are loaded while it works on the current one
+    __half s_next = __ushort_as_half(0);
+    uint32_t z_next = 0;
+    if (n_ok && grp_id < nkb) {
+      const int g0 = ((kb_begin + grp_id) * W4_BK) / p.groupsize;
+      s_next = __ldg(sp + static_cast<int64_t>(g0) * p.n);
+      z_next = static_cast<uint32_t>(__ldg(zp + static_cast<int64_t>(g0) * (p.n >> 3)));
+    }
     bool ok = true;
-    for (int kb = kb_begin; kb < kb_end && ok; ++kb) {
-      const int g = kb / steps_per_group;
-      if (g != cur_group) {
-        cur_group = g;
-        __half s = __ushort_as_half(0);
-        uint32_t z = 0;
-        if (n_ok) {
-          s = __ldg(p.scales + static_cast<int64_t>(g) * p.n + n);
-          z = (static_cast<uint32_t>(__ldg(p.qzeros + static_cast<int64_t>(g) * (p.n >> 3) + (n >> 3))) >> ((n & 7) * 4)) & 0xFu;
-        }
-        const __half zp1 = __ushort2half_rn(static_cast<unsigned short>(z + 1));
-        s2 = __half2half2(s);
-        zs2 = __half2half2(__hmul_rn(zp1, s));
+    int st = grp_id;
+    uint32_t in_ph = 0, buf = 0, w_ph = 0;
+    for (int i = grp_id; i < nkb; i += W4_GROUPS) {
+      W4Group grp;
+      grp.set(s_next, (z_next >> zshift) & 0xFu);
+      if (n_ok && i + W4_GROUPS < nkb) {
+        const int gn = ((kb_begin + i + W4_GROUPS) * W4_BK) / p.groupsize;
+        s_next = __ldg(sp + static_cast<int64_t>(gn) * p.n);
+        z_next = static_cast<uint32_t>(__ldg(zp + static_cast<int64_t>(gn) * (p.n >> 3)));
       }
-      if (!wait_or_abort(&in_full[pin.stage], pin.phase, abort_flag, 0x820) ||
-          !wait_or_abort(&w_empty[pw.stage], pw.phase ^ 1, abort_flag, 0x821)) {
+      // the operand tile is free once the group's MMAs of two steps ago are complete
+      if (!wait_or_abort(&my_w_empty[buf], w_ph ^ 1, abort_flag, 0x821)) {
         ok = false;
         break;
       }
-      const uint32_t* q = reinterpret_cast<const uint32_t*>(sQ + pin.stage * W4_RAW_BYTES) + t;
-      uint8_t* wrow = sW + pw.stage * W4_W_BYTES + row_off;
+      if (!wait_or_abort(&in_full[st], in_ph, abort_flag, 0x820)) {
+        ok = false;
+        break;
+      }
+      const uint32_t* q = reinterpret_cast<const uint32_t*>(sQ + st * W4_RAW_BYTES) + t;
+      uint8_t* wrow = w_base + buf * W4_W_BYTES + row_off;
       uint32_t words[8];
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk) words[kk] = q[kk * W4_BN];
+      for (int j = 0; j < 8; ++j) words[j] = q[j * W4_BN];
+      if (grp.fast) {
 #pragma unroll
-      for (int kk = 0; kk < 8; ++kk)
-        *reinterpret_cast<uint4*>(wrow + ((kk ^ (t & 7)) << 4)) = w4_dequant8(words[kk], s2, zs2);
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(wrow + ((j ^ (t & 7)) << 4)) = grp.expand<true>(words[j]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4*>(wrow + ((j ^ (t & 7)) << 4)) = grp.expand<false>(words[j]);
+      }
       // make the generic-proxy writes visible to the tensor core (async proxy) before signalling
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
-      if (lane == 0) mbar_arrive(&w_full[pw.stage]);
-      pin.advance_rt(in_stages);
-      pw.advance<W4_WSTAGES>();
+      if (lane == 0) mbar_arrive(&my_w_full[buf]);
+      st += W4_GROUPS;
+      if (st >= in_stages) {
+        st -= in_stages;
+        in_ph ^= 1;
+      }
+      if (++buf == W4_WBUFS) {
+        buf = 0;
+        w_ph ^= 1;
+      }
     }
 
-    // partial tile -> this CTA's shared memory as fp32 [m_pad][128] (column t contiguous across lanes)
-    float* part = reinterpret_cast<float*>(sW);
-    if (nkb > 0 && ok) ok = wait_or_abort(tfull, 0, abort_flag, 0x830);
+    // partial tile -> this CTA's shared memory as fp32 [m_pad][128] (column t contiguous across lanes);
+    // the four groups take 16-row chunks in turn and add the groups' accumulators in a fixed order
+    float* partial = reinterpret_cast<float*>(sW);
+    ok = wait_or_abort(tfull, 0, abort_flag, 0x830) && (*abort_flag == 0);
     tc_fence_after();
+    // (every group's MMAs are complete once tfull completes, so the operand tiles may be overwritten)
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    for (int c0 = 0; c0 < p.m_pad; c0 += 16) {
-      uint32_t acc[16];
-      if (nkb > 0 && ok) {
-        tmem_ld16(taddr + c0, acc);
-        tc_wait_ld();
-      } else {
+    const int used = nkb < W4_GROUPS ? nkb : W4_GROUPS;
+    for (int c0 = grp_id * 16; c0 < p.m_pad; c0 += W4_GROUPS * 16) {
+      float acc[16];
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[i] = 0u;
+      for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+      if (ok) {
+        for (int a = 0; a < used; ++a) {
+          uint32_t raw[16];
+          tmem_ld16(taddr + a * p.m_pad + c0, raw);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = (a == 0) ? __uint_as_float(raw[i]) : __fadd_rn(acc[i], __uint_as_float(raw[i]));
+        }
       }
 #pragma unroll
-      for (int i = 0; i < 16; ++i) part[(c0 + i) * W4_BN + t] = __uint_as_float(acc[i]);
+      for (int i = 0; i < 16; ++i) partial[(c0 + i) * W4_BN + t] = acc[i];
     }
   }
 
@@ -229,10 +317,11 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   cluster.sync();
 
   if (warp >= 4) {
-    const int t = threadIdx.x - 128;
+    const int t = (threadIdx.x - 128) & 127;
+    const int grp_id = (threadIdx.x - 128) >> 7;
     const int n = n0 + t;
     if (n < p.n) {
-      for (int row = rank; row < p.m; row += S) {
+      for (int row = rank + grp_id * S; row < p.m; row += W4_GROUPS * S) {
         float acc = 0.0f;
         for (int r = 0; r < S; ++r) {
           const float* remote = cluster.map_shared_rank(reinterpret_cast<float*>(sW), r);
@@ -263,8 +352,9 @@ __global__ void w4a16_dequant_kernel(const int32_t* __restrict__ qweight, const 
   const int g = (kk * 8) / groupsize;
   const __half s = scales[static_cast<int64_t>(g) * n + col];
   const uint32_t z = (static_cast<uint32_t>(qzeros[static_cast<int64_t>(g) * (n >> 3) + (col >> 3)]) >> ((col & 7) * 4)) & 0xFu;
-  const __half zs = __hmul_rn(__ushort2half_rn(static_cast<unsigned short>(z + 1)), s);
-  const uint4 v = w4_dequant8(static_cast<uint32_t>(qweight[idx]), __half2half2(s), __half2half2(zs));
+  W4Group grp;
+  grp.set(s, z);
+  const uint4 v = grp.expand_any(static_cast<uint32_t>(qweight[idx]));
   const __half* h = reinterpret_cast<const __half*>(&v);
 #pragma unroll
   for (int j = 0; j < 8; ++j) w[static_cast<int64_t>(kk * 8 + j) * ldw + col] = h[j];
@@ -286,7 +376,7 @@ int w4a16_gemm_dispatch(const void* a, int64_t lda, const int32_t* qweight, cons
                         int64_t m, int n, int k, int groupsize, void* c, int64_t ldc, int split_k, cudaStream_t st) {
   if (!a || !qweight || !scales || !qzeros || !c || m < 0 || n <= 0 || k <= 0 || groupsize <= 0) return FR_ERR_ARG;
   if (m == 0) return FR_OK;
-  if ((n % 8) || (k % W4_BK) || (groupsize % W4_BK) || (k % groupsize) || (lda % 8) || ldc < n) return FR_ERR_ALIGN;
+  if ((n % 8) || (k % W4_BK) || (groupsize % 64) || (k % groupsize) || (lda % 8) || ldc < n) return FR_ERR_ALIGN;
   if (split_k != 0 && split_k != 1 && split_k != 2 && split_k != 4 && split_k != 8) return FR_ERR_ARG;
   const DeviceInfo& di = device_info();
   const int n_tiles = (n + W4_BN - 1) / W4_BN;
@@ -304,8 +394,8 @@ int w4a16_gemm_dispatch(const void* a, int64_t lda, const int32_t* qweight, cons
   if (rc) return rc;
 
   auto kern = w4a16_gemm_kernel;
-  for (int64_t m0 = 0; m0 < m; m0 += 256) {
-    const int mc = static_cast<int>(m - m0 < 256 ? m - m0 : 256);
+  for (int64_t m0 = 0; m0 < m; m0 += W4_MAX_M) {
+    const int mc = static_cast<int>(m - m0 < W4_MAX_M ? m - m0 : W4_MAX_M);
     W4Params p = {};
     p.scales = static_cast<const __half*>(scales);
     p.qzeros = qzeros;
@@ -318,22 +408,28 @@ int w4a16_gemm_dispatch(const void* a, int64_t lda, const int32_t* qweight, cons
     p.groupsize = groupsize;
     p.x_bytes = p.m_pad * 128;
     int stages = (W4_SMEM_BUDGET - W4_WSTAGES * W4_W_BYTES) / (W4_RAW_BYTES + p.x_bytes);
-    p.in_stages = stages > W4_MAX_IN ? W4_MAX_IN : stages;
-    if (p.in_stages < 2) return FR_ERR_UNSUPPORTED;
+    const int steps = (KB + S - 1) / S;
+    if (stages > steps) stages = steps;
+    if (stages > W4_MAX_IN) stages = W4_MAX_IN;
+    // A multiple of the group count: the previous use of a stage then belongs to the same dequantising group,
+    // which keeps every waiter within one phase of its barrier.
+    p.in_stages = (stages + W4_GROUPS - 1) / W4_GROUPS * W4_GROUPS;
+    if ((W4_RAW_BYTES + p.x_bytes) * p.in_stages + W4_WSTAGES * W4_W_BYTES > W4_SMEM_BUDGET) p.in_stages -= W4_GROUPS;
+    if (p.in_stages < W4_GROUPS) return FR_ERR_UNSUPPORTED;
     uint32_t cols = 32;
-    while (cols < static_cast<uint32_t>(p.m_pad)) cols *= 2;
+    while (cols < static_cast<uint32_t>(p.m_pad * W4_GROUPS)) cols *= 2;
     p.tmem_cols = cols;
     // the partial tile (m_pad x 128 fp32) reuses the operand ring and the start of the activation ring
     if (p.m_pad * W4_BN * 4 > W4_WSTAGES * W4_W_BYTES + p.in_stages * p.x_bytes) return FR_ERR_UNSUPPORTED;
     CUtensorMap tmX;
     rc = make_tmap_2d(&tmX, static_cast<const __half*>(a) + m0 * lda, static_cast<uint64_t>(mc),
-                      static_cast<uint64_t>(k), static_cast<uint64_t>(lda), p.m_pad, W4_BK, true);
+                      static_cast<uint64_t>(k), static_cast<uint64_t>(lda), p.m_pad, 64, true);
     if (rc) return rc;
     const int smem = W4_WSTAGES * W4_W_BYTES + p.in_stages * (p.x_bytes + W4_RAW_BYTES) + 512 + 1024;
     FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles, S, 1);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(W4_THREADS);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];

@@ -263,7 +263,8 @@ int fr_gather_rows(const void* src, int64_t ld_src, const int32_t* idx, int64_t 
  * w = fp16(q)*s - fp16(z+1)*s with every operation rounded to fp16 (:83-87); fp32 accumulation.
  * The K slices are reduced in a fixed order inside one kernel (the reference adds them with fp16
  * atomics, :103), so the result is deterministic.  split_k: 0 = choose, or 1, 2, 4, 8.
- * Requirements: n % 8 == 0, k % 64 == 0, groupsize % 64 == 0, k % groupsize == 0, lda % 8 == 0. */
+ * Requirements: n % 8 == 0, k % 64 == 0, groupsize % 64 == 0, k % groupsize == 0, lda % 8 == 0.
+ * Batches above 128 rows run as consecutive launches of 128 rows. */
 int fr_w4a16_gemm(const void* a, int64_t lda, const int32_t* qweight, const void* scales, const int32_t* qzeros,
                   int64_t m, int n, int k, int groupsize, void* c, int64_t ldc, int split_k, void* stream);
 

@@ -52,7 +52,7 @@ def test_reference_kernel_golden_vectors(dev):
                     <= 9 * 2.0 ** -11 * np.maximum(np.abs(ref), 64.0)).all()
 
 
-@pytest.mark.parametrize("k,n,gs", [(64, 8, 64), (512, 64, 128), (1024, 200, 256), (4096, 4096, 128)])
+@pytest.mark.parametrize("k,n,gs", [(128, 8, 64), (512, 64, 128), (1024, 200, 256), (4096, 4096, 128)])
 def test_dequantised_weights_bit_exact(dev, k, n, gs):
     _, b, s, z = inputs(1, k, n, gs, seed=k + n)
     w = sk.dequantize(b.to(dev), s.to(dev), z.to(dev), gs)
@@ -60,6 +60,15 @@ def test_dequantised_weights_bit_exact(dev, k, n, gs):
     # the GEMM's in-kernel dequantisation: one-hot activations return weight rows exactly
     m = min(256, k)
     rows = torch.randperm(k, generator=torch.Generator().manual_seed(1))[:m]
+    if k == 1024:
+        for factor in (200.0, 1e-3, 0.0):     # scales >= 32, < 2^-9 and zero take the un-fused product path
+            s = (s.float() * factor).half()
+            w = sk.dequantize(b.to(dev), s.to(dev), z.to(dev), gs)
+            assert np.array_equal(w.cpu().numpy().view(np.uint16), oracle.w4a16.dequant(b, s, z, gs).view(np.uint16))
+        _, _, s, _ = inputs(1, k, n, gs, seed=k + n)
+        s = s * 40                            # a mix of both paths inside one matrix
+        w = sk.dequantize(b.to(dev), s.to(dev), z.to(dev), gs)
+        assert np.array_equal(w.cpu().numpy().view(np.uint16), oracle.w4a16.dequant(b, s, z, gs).view(np.uint16))
     a = torch.zeros(m, k, dtype=torch.float16)
     a[torch.arange(m), rows] = 1.0
     c = sk.matmul_split_k(a.to(dev), b.to(dev), s.to(dev), z.to(dev), gs)
@@ -103,7 +112,7 @@ def test_argument_errors(dev):
                          kw.get("n", 64), kw.get("k", 512), kw.get("gs", 128), _lib.ptr(c), 64, kw.get("split", 0), st]
     assert lib.fr_w4a16_gemm(*args(a=None)) == -1
     assert lib.fr_w4a16_gemm(*args(n=60)) == -3
-    assert lib.fr_w4a16_gemm(*args(k=480)) == -3
+    assert lib.fr_w4a16_gemm(*args(k=448)) == -3
     assert lib.fr_w4a16_gemm(*args(gs=32)) == -3
     assert lib.fr_w4a16_gemm(*args(split=3)) == -1
     assert lib.fr_w4a16_gemm(*args(m=0)) == 0
