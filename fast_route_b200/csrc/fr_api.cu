@@ -33,7 +33,7 @@ int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, i
 int router_gemm_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate_km,
                          int64_t ld_gate, int E, int topk, int renormalize, int do_topk, float* weights,
                          int32_t* ids, float* logits_out, cudaStream_t st);
-int choose_split_k(int64_t est_tiles, int KB, int sm_count);
+int choose_split_k(int64_t est_tiles, int KB, int sm_count, bool few_rows = false);
 
 constexpr int kBlockM = FR_GEMM_BLOCK_M;
 constexpr int kTileN = 256;
@@ -496,8 +496,9 @@ static SplitPlan plan_split_tokenn(int64_t n, int H, int I, int E) {
   while (box < 256 && box < 2 * avg) box <<= 1;
   const int64_t est_tt = (n < E ? n : E) + n / box;  // token tiles: one per active expert + full ones
   const int wt1 = (I + 63) / 64, wt2 = (H + 127) / 128;
-  sp.s1 = choose_split_k(est_tt * wt1, (H + kTileK - 1) / kTileK, sms);
-  sp.s2 = choose_split_k(est_tt * wt2, (I + kTileK - 1) / kTileK, sms);
+  const bool few = n <= 32;
+  sp.s1 = choose_split_k(est_tt * wt1, (H + kTileK - 1) / kTileK, sms, few);
+  sp.s2 = choose_split_k(est_tt * wt2, (I + kTileK - 1) / kTileK, sms, few);
   size_t b1 = sp.s1 > 1 ? static_cast<size_t>(sp.s1) * n * wt1 * 128 * sizeof(float) : 0;
   size_t b2 = sp.s2 > 1 ? static_cast<size_t>(sp.s2) * n * wt2 * 128 * sizeof(float) : 0;
   sp.bytes = b1 > b2 ? b1 : b2;

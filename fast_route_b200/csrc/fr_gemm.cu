@@ -480,20 +480,29 @@ static int launch_grouped(const CUtensorMap& tmA, const CUtensorMap& tmB, const 
 }
 
 // Picks how many K slices to use when there are too few tiles to fill the machine.
-int choose_split_k(int64_t est_tiles, int KB, int sm_count) {
-  if (est_tiles <= 0 || est_tiles >= 2 * sm_count) return 1;
+int choose_split_k(int64_t est_tiles, int KB, int sm_count, bool few_rows) {
+  // Below two waves any gain in wave efficiency pays.  From two to eight waves only a handful of rows (pure
+  // weight streaming, partial tiles of a few KB) make a split worth its reduction, and only if it recovers at
+  // least 8 % of the machine: a partial last wave of such tiles costs a whole tile time (1 token on 2 experts:
+  // 448 tiles = 3.03 waves).  Measured on one B200, Mixtral-8x7B shape: 1 token 165.5 -> 155.0 us, 2 tokens
+  // 274 -> 262 us; from 64 tokens on the same rule loses 2-5 %, hence the row limit.
+  if (est_tiles <= 0 || est_tiles >= (few_rows ? 8 : 2) * sm_count) return 1;
+  const bool small = est_tiles < 2 * sm_count;
   int best = 1;
-  double best_eff = 0.0;
+  double best_eff = 0.0, base_eff = 0.0;
   for (int s = 1; s <= 16; ++s) {
     if (KB / s < 4) break;
+    if (!small && s > 4) break;
     const int64_t t = est_tiles * s;
     const int64_t waves = (t + sm_count - 1) / sm_count;
     const double eff = static_cast<double>(t) / static_cast<double>(waves * sm_count);
+    if (s == 1) base_eff = eff;
     if (eff > best_eff + 0.03) {
       best_eff = eff;
       best = s;
     }
   }
+  if (!small && best_eff < base_eff + 0.08) return 1;
   return best;
 }
 
