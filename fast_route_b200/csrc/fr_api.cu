@@ -345,16 +345,13 @@ __global__ void __launch_bounds__(256) quant_rows_kernel(const uint4* __restrict
 // the E logits by counting (ties -> lower expert id) and writes the top-k and its softmax.
 // A 128-row tensor-core tile would leave 147 SMs idle and walk H serially on one.
 template <bool BF16>
-__global__ void __launch_bounds__(256) router_small_kernel(const uint16_t* __restrict__ x, int64_t ldx,
-                                                           const uint16_t* __restrict__ gate_km, int64_t ld_gate,
-                                                           int H, int E, int topk, int renormalize,
-                                                           float* __restrict__ weights, int32_t* __restrict__ ids,
-                                                           float* __restrict__ logits_out) {
-  extern __shared__ float rs[];
+__device__ __forceinline__ void router_small_body(float* rs, int64_t row, const uint16_t* __restrict__ x, int64_t ldx,
+                                                  const uint16_t* __restrict__ gate_km, int64_t ld_gate, int H, int E,
+                                                  int topk, int renormalize, float* __restrict__ weights,
+                                                  int32_t* __restrict__ ids, float* __restrict__ logits_out) {
   float* part = rs;                 // [8 warps][E]
   float* logit = rs + 8 * E;        // [E]
   float* byrank = logit + E;        // [E]
-  const int64_t row = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint16_t* xr = x + row * ldx;
   for (int e0 = 0; e0 < E; e0 += 8) {
@@ -422,6 +419,135 @@ __global__ void __launch_bounds__(256) router_small_kernel(const uint16_t* __res
     s = psum;
   }
   for (int j = lane; j < topk; j += 32) weights[row * topk + j] = __fdiv_rn(exp_recipe(__fsub_rn(byrank[j], top)), s);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) router_small_kernel(const uint16_t* __restrict__ x, int64_t ldx,
+                                                           const uint16_t* __restrict__ gate_km, int64_t ld_gate,
+                                                           int H, int E, int topk, int renormalize,
+                                                           float* __restrict__ weights, int32_t* __restrict__ ids,
+                                                           float* __restrict__ logits_out) {
+  extern __shared__ float rs[];
+  router_small_body<BF16>(rs, blockIdx.x, x, ldx, gate_km, ld_gate, H, E, topk, renormalize, weights, ids,
+                          logits_out);
+}
+
+// Decode prologue: router, align (block 16) and the row gather of a batch of at most 16 assignments in ONE launch.
+// One CTA per token routes it; the CTA that finishes last (a counter in the zeroed scratch, put back to zero) then
+// sorts the handful of assignments by expert and copies the token rows into expert order.  At this size the three
+// separate launches cost more in launch gaps than in work (router 5-12, cluster align 7, gather 4 us for 1 token).
+// Rows of a_sorted that only pad an expert's segment are left untouched: a padded row is one column of the
+// tokens-on-N GEMM tiles and never mixes into another token's results.
+constexpr int kPrologueMaxAssign = 16;
+struct PrologueParams {
+  const uint16_t* x;
+  int64_t ldx;
+  const uint16_t* gate_km;
+  int64_t ld_gate;
+  int H, E, topk, renormalize, M, bs;
+  float* weights;
+  int32_t* ids;
+  int32_t* sorted;
+  int64_t sorted_len;
+  int32_t* expert_ids;
+  int64_t expert_ids_len;
+  int32_t* num_post;
+  int32_t* counts;
+  int32_t* inv_pos;
+  uint16_t* a_sorted;      // row pitch H
+  unsigned int* counter;   // zero before the launch, zero again after it
+};
+
+template <bool BF16>
+__global__ void __launch_bounds__(256) decode_prologue_kernel(const PrologueParams p) {
+  extern __shared__ float rs[];
+  __shared__ int s_last;
+  __shared__ int s_ids[kPrologueMaxAssign];
+  __shared__ int s_pos[kPrologueMaxAssign];
+  router_small_body<BF16>(rs, blockIdx.x, p.x, p.ldx, p.gate_km, p.ld_gate, p.H, p.E, p.topk, p.renormalize,
+                          p.weights, p.ids, nullptr);
+  // publish this token's routing, then find out whether every other token is done
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(p.counter, 1u);
+    s_last = (prev == static_cast<unsigned int>(p.M) - 1u) ? 1 : 0;
+    if (s_last) *p.counter = 0u;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+
+  const int E = p.E, n = p.M * p.topk, bs = p.bs;
+  int* cnt = reinterpret_cast<int*>(rs);      // [E] counts, the router's scratch is free now
+  int* start = cnt + E;                       // [E+1] padded starts
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    int e = __ldcg(p.ids + i);
+    if (e < 0 || e >= E) {
+      report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(e));
+      e = -1;
+    }
+    s_ids[i] = e;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int c = 0;
+    for (int i = 0; i < n; ++i) c += (s_ids[i] == e) ? 1 : 0;
+    cnt[e] = c;
+    if (p.counts) p.counts[e] = c;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {     // exclusive scan of the padded counts, a chunk of experts per lane
+    const int lane = threadIdx.x;
+    const int chunk = (E + 31) / 32;
+    const int e0 = lane * chunk;
+    int sum = 0;
+    for (int e = e0; e < e0 + chunk && e < E; ++e) sum += (cnt[e] + bs - 1) / bs * bs;
+    int incl = sum;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int o = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += o;
+    }
+    int run = incl - sum;
+    for (int e = e0; e < e0 + chunk && e < E; ++e) {
+      start[e] = run;
+      run += (cnt[e] + bs - 1) / bs * bs;
+    }
+    if (lane == 31) start[E] = incl;
+  }
+  __syncthreads();
+  const int num_post = start[E];
+  // sentinels and the block -> expert table everywhere, then the valid entries on top
+  for (int64_t q = threadIdx.x; q < p.sorted_len; q += blockDim.x) p.sorted[q] = n;
+  for (int64_t b = threadIdx.x; b < p.expert_ids_len; b += blockDim.x) p.expert_ids[b] = -1;
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    for (int b = start[e] / bs; b < start[e + 1] / bs; ++b)
+      if (b < p.expert_ids_len) p.expert_ids[b] = e;
+  if (threadIdx.x < n) {
+    const int i = threadIdx.x, e = s_ids[i];
+    int pos = -1;
+    if (e >= 0) {
+      int rank = 0;
+      for (int j = 0; j < i; ++j) rank += (s_ids[j] == e) ? 1 : 0;    // stable: earlier flat index first
+      pos = start[e] + rank;
+      if (pos < p.sorted_len) p.sorted[pos] = i;
+      if (p.inv_pos) p.inv_pos[i] = pos;
+    }
+    s_pos[i] = pos;
+  }
+  if (threadIdx.x == 0) *p.num_post = num_post;
+  __syncthreads();
+  // gather: token rows into expert order, 16-byte vectors
+  const int row_v = p.H / 8;
+  for (int i = 0; i < n; ++i) {
+    const int pos = s_pos[i];
+    if (pos < 0) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(i / p.topk) * p.ldx);
+    uint4* dst = reinterpret_cast<uint4*>(p.a_sorted + static_cast<int64_t>(pos) * p.H);
+    for (int v = threadIdx.x; v < row_v; v += blockDim.x) dst[v] = __ldg(src + v);
+  }
 }
 
 constexpr int kSmallRouterRows = 32;
@@ -597,22 +723,67 @@ static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
   return w;
 }
 
+// Router + align + row gather in one launch for at most kPrologueMaxAssign assignments (see decode_prologue_kernel).
+// Returns FR_ERR_UNSUPPORTED when the case does not qualify; the caller then runs the separate stages.
+static int decode_prologue_dispatch(const void* x, int dtype, int64_t M, int H, int64_t ldx, const void* gate,
+                                    int64_t gsh, int64_t gse, int E, int topk, int renormalize, float* weights,
+                                    int32_t* ids, const ExpertWs& w, cudaStream_t st) {
+  const int64_t n = M * topk;
+  if (n > kPrologueMaxAssign || M < 1 || !use_tokenn(n, E) || E > 1024 || !w.align_ws || w.align_ws_bytes < 16)
+    return FR_ERR_UNSUPPORTED;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  // the gate must already be K-major (W_g[E,H] viewed as [H,E]); otherwise the transposing path runs
+  if (gsh != 1 || (gse % 8) || (H % 8) || (ldx % 8) || (reinterpret_cast<uintptr_t>(gate) & 15) ||
+      (reinterpret_cast<uintptr_t>(x) & 15))
+    return FR_ERR_UNSUPPORTED;
+  PrologueParams p = {};
+  p.x = static_cast<const uint16_t*>(x);
+  p.ldx = ldx;
+  p.gate_km = static_cast<const uint16_t*>(gate);
+  p.ld_gate = gse;
+  p.H = H;
+  p.E = E;
+  p.topk = topk;
+  p.renormalize = renormalize;
+  p.M = static_cast<int>(M);
+  p.bs = 16;
+  p.weights = weights;
+  p.ids = ids;
+  p.sorted = w.sorted;
+  p.sorted_len = w.sorted_len;
+  p.expert_ids = w.expert_ids;
+  p.expert_ids_len = w.expert_ids_len;
+  p.num_post = w.num_post;
+  p.counts = w.counts;
+  p.inv_pos = w.inv_pos;
+  p.a_sorted = w.a_sorted;
+  p.counter = reinterpret_cast<unsigned int*>(w.align_ws) + 2;   // after the two grid-barrier words
+  const size_t smem = static_cast<size_t>(10) * E * sizeof(float);
+  if (dtype == FR_BF16) decode_prologue_kernel<true><<<static_cast<unsigned>(M), 256, smem, st>>>(p);
+  else decode_prologue_kernel<false><<<static_cast<unsigned>(M), 256, smem, st>>>(p);
+  return static_cast<int>(cudaGetLastError());
+}
+
 // align -> permute -> GEMM1+SiLU -> GEMM2 -> combine for n assignments (flat id i belongs to
 // token i / topk) whose expert ids are in `ids`.
 static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const float* weights, const void* w1,
                         const void* w2, int dtype, int64_t M, int topk, int H, int I, int E, void* out,
                         int64_t ld_out, const ExpertWs& w, cudaStream_t st, const void* residual = nullptr,
-                        int64_t ld_res = 0) {
+                        int64_t ld_res = 0, bool prologue_done = false) {
+  // prologue_done: align outputs and a_sorted were already produced by decode_prologue_dispatch
   const int64_t n = M * topk;
   const bool tokenn = use_tokenn(n, E);
-  int rc = align_dispatch(ids, n, E, tokenn ? 16 : kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
-                          w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
-  if (rc) return rc;
+  int rc = FR_OK;
   const int row_v = H / 8;
-  permute_rows_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
-      static_cast<const uint4*>(x), ldx / 8, w.sorted, w.num_post, n, topk, reinterpret_cast<uint4*>(w.a_sorted),
-      H / 8, row_v);
-  FR_CUDA_OK(cudaGetLastError());
+  if (!prologue_done) {
+    rc = align_dispatch(ids, n, E, tokenn ? 16 : kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
+                        w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
+    if (rc) return rc;
+    permute_rows_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
+        static_cast<const uint4*>(x), ldx / 8, w.sorted, w.num_post, n, topk, reinterpret_cast<uint4*>(w.a_sorted),
+        H / 8, row_v);
+    FR_CUDA_OK(cudaGetLastError());
+  }
   if (tokenn) {
     // few tokens per expert: tokens on the MMA N axis, experts padded to 16 rows instead of 128
     rc = gemm_tokenn_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.counts, w.num_post, w.sorted,
@@ -932,8 +1103,12 @@ int fr_moe_layer(const void* x, const void* gate, int64_t gate_stride_h, int64_t
   ews.align_ws_bytes = aws_bytes;
   if (topk_weights_out) tw = topk_weights_out;
   if (topk_ids_out) ti = topk_ids_out;
-  int rc = route_fused_impl(x, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
-                            nullptr, rws, st);
+  int rc = decode_prologue_dispatch(x, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
+                                    ews, st);
+  if (rc == FR_OK) return experts_impl(x, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st, nullptr, 0, true);
+  if (rc != FR_ERR_UNSUPPORTED) return rc;
+  rc = route_fused_impl(x, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
+                        nullptr, rws, st);
   if (rc) return rc;
   return experts_impl(x, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st);
 }
@@ -1009,8 +1184,12 @@ int fr_moe_block(const void* attn_out, const void* x, const void* gamma, float e
   ews.align_ws = aws;
   ews.align_ws_bytes = aws_bytes;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = route_fused_impl(moe_in, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
-                            nullptr, rws, st);
+  int rc = decode_prologue_dispatch(moe_in, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize,
+                                    tw, ti, ews, st);
+  if (rc == FR_OK) return experts_impl(moe_in, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st, res, H, true);
+  if (rc != FR_ERR_UNSUPPORTED) return rc;
+  rc = route_fused_impl(moe_in, dtype, M, H, H, gate, gate_stride_h, gate_stride_e, E, topk, renormalize, tw, ti,
+                        nullptr, rws, st);
   if (rc) return rc;
   return experts_impl(moe_in, H, ti, tw, w1, w2, dtype, M, topk, H, I, E, out, H, ews, st, res, H);
 }

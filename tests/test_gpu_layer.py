@@ -356,3 +356,26 @@ def test_baseline_layer_with_softmax_then_topk_routing(dev, M, H, I, E, k, dt, r
     cpu_logits = (x.float() @ gate.float()).to(dt)
     _, ci, _ = oracle.softmax_topk(cpu_logits, k, renormalize=renorm)
     assert (ci == oi).all(1).mean() > 0.97
+
+
+@pytest.mark.parametrize("M,E,k", [(1, 8, 2), (2, 8, 2), (5, 8, 2), (8, 8, 2), (1, 64, 6), (2, 64, 6), (3, 16, 4),
+                                   (16, 8, 1), (4, 200, 3)])
+def test_decode_prologue_matches_separate_stages(dev, M, E, k):
+    """Batches of at most 16 assignments run router + align + row gather as one launch.  The result must be
+    bit-identical to the separately launched stages: same routing as fused_route, same layer output as the
+    experts-only entry point fed with that routing, and as the layer called with a gate layout that takes the
+    general path (row-major [H,E], which is transposed first)."""
+    H, I = 512, 384
+    for dt in (torch.bfloat16, torch.float16):
+        x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=M + E, dtype=dt, weight_std=0.05)
+        xd, gd, w1d, w2d = x.to(dev), gate.to(dev), w1.to(dev), w2.to(dev)
+        out, tw, ti = fr.fused_moe(xd, gd, w1d, w2d, k, return_routing=True)
+        rw, ri = fr.fused_route(xd, gd, k)
+        assert torch.equal(ti, ri) and torch.equal(tw, rw)
+        assert torch.equal(out, fr.fused_experts(xd, w1d, w2d, tw, ti))
+        assert torch.equal(out, fr.fused_moe(xd, gd.contiguous(), w1d, w2d, k))
+        ref, _, _ = oracle.moe_layer(x, gate, w1, w2, k, routing=(tw.cpu(), ti.cpu()))
+        check_layer(out, ref)
+        # twice more on the same workspace: the completion counter must be back at zero
+        assert torch.equal(out, fr.fused_moe(xd, gd, w1d, w2d, k))
+        assert torch.equal(out, fr.fused_moe(xd, gd, w1d, w2d, k))
