@@ -2,7 +2,7 @@
 
 Run where the reference tree is mounted:
 
-    python tests/golden/make_golden.py [/path/to/reference]
+    python tests/golden/make_golden.py /path/to/reference
 
 It executes, on the CPU:
   * the reference's stable bitonic argsort (``fast_route/fast_route/ops/stable_argsort.py:96-114``)
@@ -37,7 +37,9 @@ import torch.nn.functional as F
 import triton
 import triton.language as tl
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FAST_ROUTE_REFERENCE", "")
+if not os.path.isdir(os.path.join(REF, "fast_route")):
+    sys.exit("usage: python tests/golden/make_golden.py /path/to/the/reference/checkout")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(REF, "fast_route"))
 sys.path.insert(0, os.path.join(HERE, "..", ".."))
