@@ -129,6 +129,23 @@ def cuda_time_ms(fn, reps, warm=3):
     return statistics.median(ts), ts[0]
 
 
+def cuda_time_quantiles(fn, reps=100, warm=20):
+    """(median, p20, p80) device time in ms of fn(), like the reference's do_bench(quantiles=[0.5, 0.2, 0.8])
+    (benchmarks/fused_route/moe_bench.py:90-98)."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    ts = sorted(a.elapsed_time(b) for a, b in evs)
+    q = lambda f: ts[min(len(ts) - 1, int(f * len(ts)))]
+    return q(0.5), q(0.2), q(0.8)
+
+
 def make_weights(H, I, E, device, seed=0, dtype=torch.bfloat16, experts=None):
     """Random-init weights of the layer (N(0, 0.02^2)), generated on `device`."""
     g = torch.Generator(device=device).manual_seed(seed)
@@ -217,16 +234,19 @@ def sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms):
         x = torch.randn(M, H, device=dev, dtype=w1.dtype)
         _, _, ti = fr.fused_moe(x, wg.t(), w1, w2, k, return_routing=True)
         active = int(torch.unique(ti).numel())
-        reps = 50 if M <= 1024 else 8
-        med, _ = cuda_time_ms(lambda: fr.fused_moe(x, wg.t(), w1, w2, k), reps, warm=10 if M <= 1024 else 3)
+        # timing protocol of the reference's benches: >= 20 warm-up calls, 100 timed calls, median / p20 / p80
+        reps = 100 if M <= 4096 else 40
+        med, m20, m80 = cuda_time_quantiles(lambda: fr.fused_moe(x, wg.t(), w1, w2, k), reps, 20 if M <= 4096 else 5)
         out = torch.empty_like(x)
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g):
             out = fr.fused_moe(x, wg.t(), w1, w2, k)
-        gmed, _ = cuda_time_ms(g.replay, reps, warm=10 if M <= 1024 else 3)
+        gmed, g20, g80 = cuda_time_quantiles(g.replay, reps, 20 if M <= 4096 else 5)
         flops = synth.layer_flops(M, H, I, E, k)
         nbytes = synth.layer_bytes(active, M, H, I, E)
-        rows.append({"M": M, "ms": round(med, 4), "ms_graph": round(gmed, 4), "tokens_per_s": M / gmed * 1e3,
+        rows.append({"M": M, "ms": round(med, 4), "ms_p20_p80": [round(m20, 4), round(m80, 4)],
+                     "ms_graph": round(gmed, 4), "ms_graph_p20_p80": [round(g20, 4), round(g80, 4)],
+                     "tokens_per_s": M / gmed * 1e3,
                      "tflops": flops / gmed / 1e9, "frac_tensor_peak": flops / gmed / 1e9 / peaks["bf16_tflops"],
                      "active_experts": active, "hbm_gbs": nbytes / gmed / 1e6,
                      "frac_hbm_peak": nbytes / gmed / 1e6 / peaks["hbm_gbs"],
