@@ -45,6 +45,7 @@ struct TokenNParams {
   const float* col_scale;     // fp8 inputs only: weight scale per weight row (E * w_rows_per_expert)
   int tn_box;                 // tokens per tile = TMA box height of the token operand: 16 ... 256
   int stages;                 // pipeline depth: TPIPE_BYTES / (16 KB + tn_box * 128 B), at most TMAX_STAGES
+  int max_rows;               // rows of the token operand / output buffers
 };
 
 struct TileInfo {
@@ -96,6 +97,8 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     for (int e = 0; e < p.E; ++e) {
       int c = __ldg(p.counts + e);
       if (c < 0) c = 0;
+      // counts that do not fit the buffers (an align stage that never ran) must not turn into stores past them
+      if (c > p.max_rows - row) c = p.max_rows - row > 0 ? p.max_rows - row : 0;
       ex_start[e] = row;
       ex_count[e] = c;
       ex_tile0[e] = tile;
@@ -359,6 +362,7 @@ int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, i
 
   TokenNParams p = {};
   p.counts = counts;
+  p.max_rows = static_cast<int>(max_rows < 0x7fffffff ? max_rows : 0x7fffffff);
   p.sorted_ids = sorted_ids;
   p.topk_w = topk_w;
   p.n_valid = n_valid;
