@@ -414,6 +414,7 @@ def gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps):
             "achieved": flops / med / 1e9, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
             "frac": flops / med / 1e9 / peaks["bf16_tflops"],
             "frac_of_sustained_peak": flops / med / 1e9 / peaks["bf16_tflops_sustained"],
+            "frac_of_datasheet_peak": flops / med / 1e9 / 2250.0,
             "peak_source": peaks["source"] + " (burst cuBLAS bf16; kernel timed alone)",
             "ms_per_launch": med, "algorithmic_flops_per_launch": flops, "traffic": None}
 
@@ -580,6 +581,12 @@ def run_ours(args, rank, world, local_rank):
         if not args.no_cpu:
             cb = cpu_reference_rate(H, I, E, k, args.cpu_tokens, 3, warm=1, weights=(wg, w1, w2), budget_s=20.0)
             line["cpu_baseline"] = {k_: cb[k_] for k_ in ("value", "unit", "cores", "kind", "sample")}
+            # the reference's own CPU-runnable case (fp32, 256 tokens, H=1024, I=2048, 8 experts, top-2)
+            c1 = cpu_reference_rate(1024, 2048, 8, 2, 256, 10, warm=3)
+            line["cpu_reference_small_case"] = {
+                "value": c1["value"], "unit": "tokens/s", "cores": c1["cores"], "ms": c1["ms_per_sample"],
+                "gflops": (2.0 * 1024 * 8 + 6.0 * 2 * 1024 * 2048) * c1["value"] / 1e9,
+                "config": "M=256 H=1024 I=2048 E=8 top-2 fp32, 3 warm-up + 10 timed passes, median"}
     _lib.raise_on_device_error()
     print(json.dumps(line), flush=True)
 
