@@ -658,7 +658,12 @@ static int route_fused_impl(const void* x, int dtype, int64_t M, int H, int64_t 
     gate_km = ws.gate_km;
     ld_gate = ws.ld_gate;
   }
-  if (M <= kSmallRouterRows && (H % 8) == 0 && (ldx % 8) == 0 && (ld_gate % 8) == 0 && E <= 1024 &&
+  // The tensor-core router walks H serially in every CTA (about 23 us for H = 4096 whatever the batch), so the
+  // one-CTA-per-token kernel also takes the mid-size batches for which its M*E*H multiply-adds cost less than that
+  // (measured crossover: 2048 tokens at E = 8, H = 4096; 512 tokens at E = 64, H = 2048).  The two kernels add in
+  // different orders, so the last bits of a token's logits depend on which one its batch size selects.
+  const bool gemv = M <= kSmallRouterRows || static_cast<int64_t>(M) * E * H < (int64_t(1) << 26);
+  if (gemv && (H % 8) == 0 && (ldx % 8) == 0 && (ld_gate % 8) == 0 && E <= 1024 &&
       (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(gate_km) & 15) == 0) {
     const size_t smem = static_cast<size_t>(10) * E * sizeof(float);
     if (dtype == FR_BF16)
