@@ -556,7 +556,8 @@ def run_ours(args, rank, world, local_rank):
         "config": {"workload": f"{args.workload} MoE layer H={H} I={I} E={E} top-{k}, M={M} tokens per GPU per step",
                    "parallelism": "single GPU" if world == 1 else
                    f"expert parallel ep{world} + token data parallel, rows moved by {args.ep_mode}",
-                   "l2": "weights (2.8 GB) and activations far exceed the 126 MB L2; no explicit flush",
+                   "l2": f"expert weights ({3.0 * E * H * I * 2 / 1e9:.1f} GB) and activations far exceed the 126 MB L2; "
+                         "no explicit flush",
                    "tokens_per_step_total": total_tokens},
         "tflops": flops / ms_per_step / 1e9,
         "frac_tensor_peak": flops / ms_per_step / 1e9 / (peaks["bf16_tflops_sustained"] * world),
