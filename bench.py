@@ -518,23 +518,26 @@ def run_ours(args, rank, world, local_rank):
         return
 
     # ---- end to end through the public API with host buffers ------------------------
+    # Every step copies its own input batch from pinned host memory and its result back.  The calls are pipelined
+    # the way a serving loop issues them: step i+1's input travels while step i computes, step i's result travels
+    # while step i+1 computes; the timed region ends after the last result has arrived.
     hx = [torch.randn(M, H, dtype=dtype).pin_memory() for _ in range(2)]
-    hout = torch.empty(M, H, dtype=dtype).pin_memory()
-    dx = torch.empty(M, H, dtype=dtype, device=dev)
+    hout = [torch.empty(M, H, dtype=dtype).pin_memory() for _ in range(2)]
 
     def e2e_step(i):
-        if world == 1:      # the host-buffer entry point: chunked, copies overlapped with compute
-            fr.fused_moe_host(hx[i % 2], wg.t(), w1, w2, k, out_host=hout)
+        if world == 1:
+            fr.fused_moe_host(hx[i % 2], wg.t(), w1, w2, k, out_host=hout[i % 2], chunk=M, pipelined=True)
         else:
-            dx.copy_(hx[i % 2], non_blocking=True)
-            out = layer(dx)
-            hout.copy_(out, non_blocking=True)
+            ep.fused_moe_ep_host(hx[i % 2], wg.t(), w1, w2, k, group, out_host=hout[i % 2],
+                                 p2p=(args.ep_mode == "p2p"), pipelined=True)
     for i in range(max(1, min(args.warmup, 3))):
         e2e_step(i)
+    fr.fused_moe_host_wait(dev)
     barrier()
     e0.record()
     for i in range(args.steps):
         e2e_step(i)
+    fr.fused_moe_host_wait(dev)
     e1.record()
     barrier()
     ems = e0.elapsed_time(e1)

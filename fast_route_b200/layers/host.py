@@ -31,52 +31,83 @@ def _plan(M: int, chunk: int):
     return [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
 
 
-def fused_moe_host(x_host: torch.Tensor, gate: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk: int,
-                   out_host: torch.Tensor = None, renormalize: bool = True, chunk: int = 6144) -> torch.Tensor:
-    """``x_host[M,H]`` (pinned CPU memory, fp16/bf16) -> ``out_host[M,H]`` (pinned CPU memory).
-
-    Weights and gate are device tensors as for ``fused_moe``.  The copies are asynchronous:
-    synchronise the current stream (or the device) before reading ``out_host``.
-    """
-    assert not x_host.is_cuda and x_host.is_pinned(), "x_host must be pinned host memory"
-    assert x_host.dim() == 2 and x_host.is_contiguous()
-    dev = w1.device
+def host_pipeline(fn, x_host: torch.Tensor, out_host: torch.Tensor, dev: torch.device, chunk: int,
+                  pipelined: bool, tag: str = "layer") -> torch.Tensor:
+    """Streams ``x_host`` through ``fn`` (device tensor ``[rows,H]`` -> device tensor ``[rows,H]``, possibly the same
+    storage) chunk by chunk: copy-in, ``fn`` and copy-out run on three streams and meet through events only."""
     M, H = x_host.shape
-    if out_host is None:
-        out_host = torch.empty_like(x_host).pin_memory()
-    assert out_host.is_pinned() and out_host.shape == x_host.shape and out_host.dtype == x_host.dtype
     plan = _plan(M, chunk)
     rows = max(b - a for a, b in plan)
-    key = (dev.index, H, x_host.dtype)
+    key = (dev.index, H, x_host.dtype, tag)
     st = _state.get(key)
     if st is None or st["bufs"][0].shape[0] < rows:
+        if st is not None:
+            st["s_out"].synchronize()                # the old buffers may still be on their way out
         st = {"s_in": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev),
-              "bufs": [torch.empty(rows, H, dtype=x_host.dtype, device=dev) for _ in range(3)]}
+              "bufs": [torch.empty(rows, H, dtype=x_host.dtype, device=dev) for _ in range(3)],
+              "free": [None, None, None], "next": 0}
         _state[key] = st
-    s_in, s_out, bufs = st["s_in"], st["s_out"], st["bufs"]
+    s_in, s_out, bufs, free = st["s_in"], st["s_out"], st["bufs"], st["free"]
     cur = torch.cuda.current_stream(dev)
-    s_in.wait_stream(cur)
-    s_out.wait_stream(cur)
+    if not pipelined:
+        s_in.wait_stream(cur)
     nb = len(bufs)
-    ev_in, ev_out = [], []
-    for i, (lo, hi) in enumerate(plan):
-        buf = bufs[i % nb][:hi - lo]
+    for lo, hi in plan:
+        b = st["next"] % nb
+        st["next"] += 1
+        buf = bufs[b][:hi - lo]
         with torch.cuda.stream(s_in):
-            if i >= nb:
-                s_in.wait_event(ev_out[i - nb])          # the buffer's previous result has left the device
+            if free[b] is not None:
+                s_in.wait_event(free[b])             # the buffer's previous result has left the device
             buf.copy_(x_host[lo:hi], non_blocking=True)
-            e = torch.cuda.Event()
-            e.record(s_in)
-            ev_in.append(e)
-        cur.wait_event(ev_in[i])
-        fused_moe(buf, gate, w1, w2, topk, renormalize=renormalize, inplace=True)
+            ev_in = torch.cuda.Event()
+            ev_in.record(s_in)
+        cur.wait_event(ev_in)
+        res = fn(buf)
         done = torch.cuda.Event()
         done.record(cur)
         with torch.cuda.stream(s_out):
             s_out.wait_event(done)
-            out_host[lo:hi].copy_(buf, non_blocking=True)
+            out_host[lo:hi].copy_(res, non_blocking=True)
+            if res.data_ptr() != buf.data_ptr():
+                res.record_stream(s_out)             # keep the result's memory until it has left the device
             e = torch.cuda.Event()
             e.record(s_out)
-            ev_out.append(e)
-    cur.wait_stream(s_out)
+            free[b] = e
+    if not pipelined:
+        cur.wait_stream(s_out)
     return out_host
+
+
+def fused_moe_host(x_host: torch.Tensor, gate: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk: int,
+                   out_host: torch.Tensor = None, renormalize: bool = True, chunk: int = 6144,
+                   pipelined: bool = False) -> torch.Tensor:
+    """``x_host[M,H]`` (pinned CPU memory, fp16/bf16) -> ``out_host[M,H]`` (pinned CPU memory).
+
+    Weights and gate are device tensors as for ``fused_moe``.  The copies are asynchronous:
+    synchronise the current stream (or the device) before reading ``out_host``.
+
+    ``pipelined=True`` lets consecutive calls overlap as a serving loop wants them to: the copy-in does not
+    wait for earlier work on the current stream (``x_host`` must be ready when the call is made) and the current
+    stream does not wait for the copy-out, so the next call's input travels while this call computes and this
+    call's result travels while the next one computes.  Call ``fused_moe_host_wait()`` (or synchronise the
+    device) before reading any ``out_host`` of such calls.  With calls that overlap like this one chunk per call
+    (``chunk >= M``) is fastest; chunking inside a call only pays when calls are isolated.
+    """
+    assert not x_host.is_cuda and x_host.is_pinned(), "x_host must be pinned host memory"
+    assert x_host.dim() == 2 and x_host.is_contiguous()
+    dev = w1.device
+    if out_host is None:
+        out_host = torch.empty_like(x_host).pin_memory()
+    assert out_host.is_pinned() and out_host.shape == x_host.shape and out_host.dtype == x_host.dtype
+    return host_pipeline(lambda buf: fused_moe(buf, gate, w1, w2, topk, renormalize=renormalize, inplace=True),
+                         x_host, out_host, dev, chunk, pipelined)
+
+
+def fused_moe_host_wait(device=None) -> None:
+    """Makes the current stream wait for the copy-outs of all earlier ``fused_moe_host`` calls on ``device``."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    cur = torch.cuda.current_stream(dev)
+    for key, st in _state.items():
+        if key[0] == dev.index:
+            cur.wait_stream(st["s_out"])

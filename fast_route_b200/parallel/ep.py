@@ -287,3 +287,19 @@ def fused_moe_ep_p2p(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: 
 def ctypes_ptr(addr: int):
     import ctypes
     return ctypes.c_void_p(int(addr))
+
+
+def fused_moe_ep_host(x_host: torch.Tensor, gate: torch.Tensor, w1_local: torch.Tensor, w2_local: torch.Tensor,
+                      topk: int, group: "ExpertParallelGroup", out_host: torch.Tensor = None, p2p: bool = True,
+                      pipelined: bool = False) -> torch.Tensor:
+    """The expert-parallel layer for a rank whose token batch lives in pinned host memory: copy-in, the layer
+    (``fused_moe_ep_p2p`` or ``fused_moe_ep``) and copy-out on three streams, one chunk per call.  ``pipelined``
+    as in ``layers.host.fused_moe_host``: consecutive calls overlap; ``fused_moe_host_wait()`` before reading."""
+    from ..layers.host import host_pipeline
+    assert not x_host.is_cuda and x_host.is_pinned() and x_host.dim() == 2 and x_host.is_contiguous()
+    dev = w1_local.device
+    if out_host is None:
+        out_host = torch.empty_like(x_host).pin_memory()
+    fn = (lambda buf: fused_moe_ep_p2p(buf, gate, w1_local, w2_local, topk, group)) if p2p else \
+         (lambda buf: fused_moe_ep(buf, gate, w1_local, w2_local, topk, group))
+    return host_pipeline(fn, x_host, out_host, dev, x_host.shape[0], pipelined, tag="ep")

@@ -379,3 +379,21 @@ def test_decode_prologue_matches_separate_stages(dev, M, E, k):
         # twice more on the same workspace: the completion counter must be back at zero
         assert torch.equal(out, fr.fused_moe(xd, gd, w1d, w2d, k))
         assert torch.equal(out, fr.fused_moe(xd, gd, w1d, w2d, k))
+
+
+def test_host_buffer_pipelined_calls(dev):
+    """Consecutive pipelined calls overlap their copies with one another's compute; after
+    fused_moe_host_wait every result must be complete and equal to the device layer, also when buffers are
+    reused many times and batch sizes change between calls."""
+    H, I, E, k = 512, 384, 8, 2
+    _, gate, w1, w2 = synth.moe_inputs(8, H, I, E, seed=13, dtype=torch.bfloat16, weight_std=0.05)
+    gd, w1d, w2d = gate.to(dev), w1.to(dev), w2.to(dev)
+    sizes = [2048, 2048, 700, 2048, 4096, 33, 2048, 2048]
+    xs = [synth.randn((m, H), 14, i).to(torch.bfloat16).pin_memory() for i, m in enumerate(sizes)]
+    outs = [torch.empty_like(x).pin_memory() for x in xs]
+    for x, o in zip(xs, outs):
+        fr.fused_moe_host(x, gd, w1d, w2d, k, out_host=o, chunk=1 << 20, pipelined=True)
+    fr.fused_moe_host_wait(dev)
+    torch.cuda.synchronize()
+    for x, o in zip(xs, outs):
+        assert torch.equal(o, fr.fused_moe(x.to(dev), gd, w1d, w2d, k).cpu())
