@@ -31,10 +31,29 @@ def _plan(M: int, chunk: int):
     return [(a, b) for a, b in zip(cuts[:-1], cuts[1:]) if b > a]
 
 
+def _copy_out(st, item):
+    """Queues one deferred copy-out on the state's output stream and marks its device buffer free afterwards."""
+    res, dst, done, b, own = item
+    s_out = st["s_out"]
+    with torch.cuda.stream(s_out):
+        s_out.wait_event(done)
+        dst.copy_(res, non_blocking=True)
+        if not own:
+            res.record_stream(s_out)                 # keep the result's memory until it has left the device
+        e = torch.cuda.Event()
+        e.record(s_out)
+        st["free"][b] = e
+
+
 def host_pipeline(fn, x_host: torch.Tensor, out_host: torch.Tensor, dev: torch.device, chunk: int,
                   pipelined: bool, tag: str = "layer") -> torch.Tensor:
     """Streams ``x_host`` through ``fn`` (device tensor ``[rows,H]`` -> device tensor ``[rows,H]``, possibly the same
-    storage) chunk by chunk: copy-in, ``fn`` and copy-out run on three streams and meet through events only."""
+    storage) chunk by chunk: copy-in, ``fn`` and copy-out run on three streams and meet through events only.
+
+    Pipelined calls queue their copy-out one call late, after the next call's ``fn`` has been issued: a large
+    device-to-host copy queued earlier would sit in the copy engine in front of the few bytes a layer may read back
+    to the host on its way (the expert-parallel layer reads its split sizes), and stall that layer for the length
+    of the copy (measured with two GPUs: 11.5 instead of 9.4 ms per step)."""
     M, H = x_host.shape
     plan = _plan(M, chunk)
     rows = max(b - a for a, b in plan)
@@ -42,14 +61,19 @@ def host_pipeline(fn, x_host: torch.Tensor, out_host: torch.Tensor, dev: torch.d
     st = _state.get(key)
     if st is None or st["bufs"][0].shape[0] < rows:
         if st is not None:
+            if st["pending"] is not None:
+                _copy_out(st, st["pending"])
             st["s_out"].synchronize()                # the old buffers may still be on their way out
         st = {"s_in": torch.cuda.Stream(dev), "s_out": torch.cuda.Stream(dev),
               "bufs": [torch.empty(rows, H, dtype=x_host.dtype, device=dev) for _ in range(3)],
-              "free": [None, None, None], "next": 0}
+              "free": [None, None, None], "next": 0, "pending": None}
         _state[key] = st
     s_in, s_out, bufs, free = st["s_in"], st["s_out"], st["bufs"], st["free"]
     cur = torch.cuda.current_stream(dev)
     if not pipelined:
+        if st["pending"] is not None:
+            _copy_out(st, st["pending"])
+            st["pending"] = None
         s_in.wait_stream(cur)
     nb = len(bufs)
     for lo, hi in plan:
@@ -66,14 +90,13 @@ def host_pipeline(fn, x_host: torch.Tensor, out_host: torch.Tensor, dev: torch.d
         res = fn(buf)
         done = torch.cuda.Event()
         done.record(cur)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(done)
-            out_host[lo:hi].copy_(res, non_blocking=True)
-            if res.data_ptr() != buf.data_ptr():
-                res.record_stream(s_out)             # keep the result's memory until it has left the device
-            e = torch.cuda.Event()
-            e.record(s_out)
-            free[b] = e
+        item = (res, out_host[lo:hi], done, b, res.data_ptr() == buf.data_ptr())
+        if pipelined:
+            if st["pending"] is not None:
+                _copy_out(st, st["pending"])
+            st["pending"] = item
+        else:
+            _copy_out(st, item)
     if not pipelined:
         cur.wait_stream(s_out)
     return out_host
@@ -90,8 +113,9 @@ def fused_moe_host(x_host: torch.Tensor, gate: torch.Tensor, w1: torch.Tensor, w
     ``pipelined=True`` lets consecutive calls overlap as a serving loop wants them to: the copy-in does not
     wait for earlier work on the current stream (``x_host`` must be ready when the call is made) and the current
     stream does not wait for the copy-out, so the next call's input travels while this call computes and this
-    call's result travels while the next one computes.  Call ``fused_moe_host_wait()`` (or synchronise the
-    device) before reading any ``out_host`` of such calls.  With calls that overlap like this one chunk per call
+    call's result travels while the next one computes (its copy-out is queued during the next call).  Call
+    ``fused_moe_host_wait()`` and then synchronise before reading any ``out_host`` of such calls: it queues the last
+    copy-out and makes the current stream wait for all of them.  With calls that overlap like this one chunk per call
     (``chunk >= M``) is fastest; chunking inside a call only pays when calls are isolated.
     """
     assert not x_host.is_cuda and x_host.is_pinned(), "x_host must be pinned host memory"
@@ -110,4 +134,7 @@ def fused_moe_host_wait(device=None) -> None:
     cur = torch.cuda.current_stream(dev)
     for key, st in _state.items():
         if key[0] == dev.index:
+            if st["pending"] is not None:
+                _copy_out(st, st["pending"])
+                st["pending"] = None
             cur.wait_stream(st["s_out"])

@@ -294,7 +294,8 @@ def fused_moe_ep_host(x_host: torch.Tensor, gate: torch.Tensor, w1_local: torch.
                       pipelined: bool = False) -> torch.Tensor:
     """The expert-parallel layer for a rank whose token batch lives in pinned host memory: copy-in, the layer
     (``fused_moe_ep_p2p`` or ``fused_moe_ep``) and copy-out on three streams, one chunk per call.  ``pipelined``
-    as in ``layers.host.fused_moe_host``: consecutive calls overlap; ``fused_moe_host_wait()`` before reading."""
+    as in ``layers.host.fused_moe_host``: consecutive calls overlap; ``fused_moe_host_wait()``, then a
+    synchronisation, before reading."""
     from ..layers.host import host_pipeline
     assert not x_host.is_cuda and x_host.is_pinned() and x_host.dim() == 2 and x_host.is_contiguous()
     dev = w1_local.device
