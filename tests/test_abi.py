@@ -79,3 +79,18 @@ def test_cpu_tensors_are_rejected_loudly():
     with pytest.raises(RuntimeError):
         fr.fused_moe(x, torch.zeros(64, 4, dtype=torch.bfloat16), torch.zeros(4, 128, 64, dtype=torch.bfloat16),
                      torch.zeros(4, 64, 64, dtype=torch.bfloat16), 2)
+
+
+def test_host_chunk_plan_covers_the_batch_exactly():
+    """The chunk plan of the host-buffer entry point: contiguous, non-empty, no overlap, every row once; short first
+    and last chunks when a batch is split."""
+    from fast_route_b200.layers.host import _plan
+    for M in (1, 5, 255, 256, 1000, 6144, 6145, 7000, 8192, 16384, 16385, 100000):
+        for chunk in (256, 1024, 6144, 1 << 20):
+            plan = _plan(M, chunk)
+            assert plan[0][0] == 0 and plan[-1][1] == M
+            assert all(a < b for a, b in plan)
+            assert all(plan[i][1] == plan[i + 1][0] for i in range(len(plan) - 1))
+            assert max(b - a for a, b in plan) <= chunk + max(256, chunk // 4)
+            if M <= chunk:
+                assert plan == [(0, M)]
