@@ -75,7 +75,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint32_t kWaitBudget = 1u << 24;
 
 // ----------------------------------------------------------------------------------
-// TMA (cp.async.bulk.tensor), 2-D tiles, no multicast anywhere in this library.
+// TMA (cp.async.bulk.tensor), 2-D tiles; every CTA loads its own operands.
 // ----------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");

@@ -10,7 +10,7 @@
 //
 // Thread roles in both kernels (192 threads): warp 0 = TMA producer (one lane),
 // warp 1 = TMEM owner + MMA issuer (one lane), warps 2..5 = epilogue (warp w reads the
-// TMEM lane quarter w % 4).  No cluster multicast is used anywhere.
+// TMEM lane quarter w % 4).  Every CTA loads its own operands.
 #include "fr_common.cuh"
 
 namespace fr {
