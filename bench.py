@@ -419,6 +419,28 @@ def gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps):
             "ms_per_launch": med, "algorithmic_flops_per_launch": flops, "traffic": None}
 
 
+def bind_to_gpu_numa_node(index):
+    """Pins this process to the CPUs of the NUMA node the GPU hangs off, so that the pinned host buffers it allocates
+    next (first touch) and the copy threads sit next to the GPU's PCIe root.  Returns the node or None."""
+    try:
+        p = torch.cuda.get_device_properties(index)
+        bdf = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except Exception:
+        return None
+
+
 def run_ours(args, rank, world, local_rank):
     import fast_route_b200 as fr
     from fast_route_b200 import synth, _lib
@@ -439,7 +461,10 @@ def run_ours(args, rank, world, local_rank):
         print(json.dumps({"w4a16_splitk_gemm": w4a16_splitk(dev, peaks)}), flush=True)
         return
 
+    numa_node = None
     if world > 1:
+        # one process per GPU: keep each process (and the pinned buffers it allocates) on its GPU's NUMA node
+        numa_node = bind_to_gpu_numa_node(local_rank)
         from fast_route_b200.parallel import ep
         assert E % world == 0, "experts must divide over the ranks"
         group = ep.ExpertParallelGroup(dist.group.WORLD, E)
@@ -558,6 +583,8 @@ def run_ours(args, rank, world, local_rank):
     e2e = {"value": total_tokens / (ems / args.steps) * 1e3, "unit": "tokens/s",
            "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2 * world,
            "ms_per_step": ems / args.steps}
+    if numa_node is not None:
+        e2e["host_numa_node_rank0"] = numa_node
 
     if rank != 0:
         return
