@@ -349,29 +349,39 @@ __device__ __forceinline__ void router_small_body(float* rs, int64_t row, const 
                                                   const uint16_t* __restrict__ gate_km, int64_t ld_gate, int H, int E,
                                                   int topk, int renormalize, float* __restrict__ weights,
                                                   int32_t* __restrict__ ids, float* __restrict__ logits_out) {
-  float* part = rs;                 // [8 warps][E]
+  float* part = rs;                 // [H splits][E]
   float* logit = rs + 8 * E;        // [E]
   float* byrank = logit + E;        // [E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint16_t* xr = x + row * ldx;
-  for (int e0 = 0; e0 < E; e0 += 8) {
+  // The 8 warps form eg expert groups x hs splits of H (eg * hs = 8): a warp accumulates 8 experts over its share
+  // of H, so one pass covers 8 * eg experts (E = 8: all warps split H; E >= 64: every warp walks all of H for its
+  // own 8 experts and 64 experts take one pass instead of eight).
+  int eg = 1;
+  while (eg < 8 && eg * 8 < E) eg <<= 1;
+  const int hs = 8 / eg;
+  const int g = warp % eg, sidx = warp / eg;
+  for (int ec = 0; ec < E; ec += 8 * eg) {
+    const int e0 = ec + g * 8;
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-    for (int h = threadIdx.x * 8; h < H; h += 256 * 8) {
-      const uint4 xv = *reinterpret_cast<const uint4*>(xr + h);
-      const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    if (e0 < E) {
+      for (int h = (sidx * 32 + lane) * 8; h < H; h += hs * 32 * 8) {
+        const uint4 xv = *reinterpret_cast<const uint4*>(xr + h);
+        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        if (e0 + i < E) {
-          const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gate_km + static_cast<int64_t>(e0 + i) * ld_gate + h));
-          const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+        for (int i = 0; i < 8; ++i) {
+          if (e0 + i < E) {
+            const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gate_km + static_cast<int64_t>(e0 + i) * ld_gate + h));
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const float2 a = unpack2<BF16>(xw[q]);
-            const float2 b = unpack2<BF16>(gw[q]);
-            acc[i] = fmaf(a.x, b.x, acc[i]);
-            acc[i] = fmaf(a.y, b.y, acc[i]);
+            for (int q = 0; q < 4; ++q) {
+              const float2 a = unpack2<BF16>(xw[q]);
+              const float2 b = unpack2<BF16>(gw[q]);
+              acc[i] = fmaf(a.x, b.x, acc[i]);
+              acc[i] = fmaf(a.y, b.y, acc[i]);
+            }
           }
         }
       }
@@ -380,13 +390,13 @@ __device__ __forceinline__ void router_small_body(float* rs, int64_t row, const 
     for (int i = 0; i < 8; ++i) {
       float v = acc[i];
       for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-      if (lane == 0 && e0 + i < E) part[warp * E + e0 + i] = v;
+      if (lane == 0 && e0 + i < E) part[sidx * E + e0 + i] = v;
     }
   }
   __syncthreads();
   for (int e = threadIdx.x; e < E; e += 256) {
     float v = 0.0f;
-    for (int w = 0; w < 8; ++w) v += part[w * E + e];
+    for (int w = 0; w < hs; ++w) v += part[w * E + e];
     if (v != v) v = -INFINITY;
     logit[e] = v;
     if (logits_out) logits_out[row * E + e] = v;
