@@ -51,8 +51,9 @@ SIGNATURES = {
     "fr_moe_experts_workspace_bytes": (_Z, [_L, _I, _I, _I]),
     "fr_moe_experts": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _P, _Z, _P]),
     "fr_moe_experts_rows_cap": (_L, [_L, _I]),
-    "fr_moe_experts_peer": (_I, [_P, _L, _I, _L, _P, _P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _L, _P, _P, _Z, _P]),
-    "fr_combine_peer": (_I, [_P, _L, _I, _L, _I, _P, _P, _L, _I, _I, _P, _L, _P]),
+    "fr_ep_workspace_bytes": (_Z, [_L, _I, _I, _I]),
+    "fr_ep_experts": (_I, [_P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _P, _P, _P, _I, _I, _I, _I, _P, _L, _P, _P, _Z, _P]),
+    "fr_ep_combine": (_I, [_P, _I, _L, _L, _L, _I, _P, _P, _P, _L, _I, _I, _I, _P, _L, _P]),
     "fr_gather_rows": (_I, [_P, _L, _P, _L, _I, _P, _L, _P]),
     "fr_w4a16_gemm": (_I, [_P, _L, _P, _P, _P, _L, _I, _I, _I, _P, _L, _I, _P]),
     "fr_w4a16_dequant": (_I, [_P, _P, _P, _I, _I, _I, _P, _L, _P]),
@@ -121,7 +122,8 @@ def device_status():
 def raise_on_device_error() -> None:
     code, detail, block, count = device_status()
     if code:
-        names = {1: "bounded wait expired", 2: "expert id out of range", 3: "bad sorted id"}
+        names = {1: "bounded wait expired", 2: "expert id out of range", 3: "bad sorted id",
+                 4: "expert-parallel receive capacity exceeded"}
         raise FastRouteError(f"device status: {names.get(code, code)} (detail {detail:#x}, block {block}, "
                              f"{count} reports)")
 

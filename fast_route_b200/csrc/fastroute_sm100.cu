@@ -5,4 +5,5 @@
 #include "fr_gemm.cu"
 #include "fr_gemm_tokenn.cu"
 #include "fr_w4a16.cu"
+#include "fr_ep.cu"
 #include "fr_api.cu"

@@ -21,10 +21,10 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st, int* deferred_split, const QuantArgs* quant);
+                          cudaStream_t st, int* deferred_split, const QuantArgs* quant, int64_t rows_hint);
 int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, int64_t partial_cols,
-                             const float* topk_w, int64_t M, int topk, int dtype, const void* residual,
-                             int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st);
+                             const float* topk_w, const int32_t* inv_pos, int64_t M, int topk, int dtype,
+                             const void* residual, int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st);
 int gemm_tokenn_dispatch(int which, const void* a, int64_t lda, const void* w, int dtype, int64_t max_rows, int K,
                          int n_out, int E, int w_rows_per_expert, const int32_t* counts, const int32_t* num_post,
                          const int32_t* sorted_ids, const float* topk_w, int64_t n_valid, void* out, int64_t ldo,
@@ -121,68 +121,6 @@ __global__ void transpose_gate_kernel(const uint16_t* __restrict__ gate, int64_t
   const int e = static_cast<int>(i / ld);
   const int h = static_cast<int>(i % ld);
   out[i] = h < H ? gate[h * sh + e * se] : static_cast<uint16_t>(0);
-}
-
-// Expert-parallel dispatch fused into the gather: row p of the expert-sorted A operand is read
-// straight from the memory of the GPU that owns the token (peer pointers over NVLink, plain
-// 16-byte loads; the local GPU is just one more entry of the table).
-//   a_sorted[p,:] = peer_base[src_rank[r]][src_row[r], :],  r = sorted_ids[p]
-__global__ void __launch_bounds__(256) permute_rows_peer_kernel(const uint4* const* __restrict__ peer_base,
-                                                                int64_t ld_src_v, int world, int64_t peer_rows,
-                                                                const int32_t* __restrict__ src_rank,
-                                                                const int32_t* __restrict__ src_row,
-                                                                const int32_t* __restrict__ sorted_ids,
-                                                                const int32_t* __restrict__ num_post, int64_t n,
-                                                                uint4* __restrict__ dst, int64_t ld_dst_v, int row_v) {
-  const int64_t row = blockIdx.x;
-  if (row >= __ldg(num_post)) return;
-  const int32_t sid = __ldg(sorted_ids + row);
-  uint4* d = dst + row * ld_dst_v;
-  bool ok = sid >= 0 && sid < n;
-  int r = 0, t = 0;
-  if (ok) {
-    r = __ldg(src_rank + sid);
-    t = __ldg(src_row + sid);
-    ok = r >= 0 && r < world && t >= 0 && t < peer_rows;
-    if (!ok && threadIdx.x == 0) report(ST_BAD_SORTED_ID, static_cast<unsigned int>(sid));
-  }
-  if (ok) {
-    const uint4* s = peer_base[r] + static_cast<int64_t>(t) * ld_src_v;
-    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = s[v];
-  } else {
-    for (int v = threadIdx.x; v < row_v; v += blockDim.x) d[v] = make_uint4(0, 0, 0, 0);
-  }
-}
-
-// Expert-parallel return fused into the combine: the k result rows of a token are read from the
-// GPUs that computed them.  out[t,:] = sum_j peer_y[rank_of[t*k+j]][pos_of[t*k+j], :]
-template <bool BF16>
-__global__ void __launch_bounds__(256) combine_peer_kernel(const uint4* const* __restrict__ peer_y, int64_t ld_y_v,
-                                                           int world, int64_t peer_rows,
-                                                           const int32_t* __restrict__ rank_of,
-                                                           const int32_t* __restrict__ pos_of, int topk, int row_v,
-                                                           uint4* __restrict__ out, int64_t ld_out_v) {
-  const int64_t t = blockIdx.x;
-  for (int v = threadIdx.x; v < row_v; v += blockDim.x) {
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-    for (int j = 0; j < topk; ++j) {
-      const int r = __ldg(rank_of + t * topk + j);
-      const int pos = __ldg(pos_of + t * topk + j);
-      if (r < 0 || r >= world || pos < 0 || pos >= peer_rows) continue;
-      const uint4 raw = peer_y[r][static_cast<int64_t>(pos) * ld_y_v + v];
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = unpack2<BF16>(w[i]);
-        acc[2 * i] += f.x;
-        acc[2 * i + 1] += f.y;
-      }
-    }
-    out[t * ld_out_v + v] = make_uint4(pack2<BF16>(acc[0], acc[1]), pack2<BF16>(acc[2], acc[3]),
-                                       pack2<BF16>(acc[4], acc[5]), pack2<BF16>(acc[6], acc[7]));
-  }
 }
 
 // Residual add and RMSNorm in one pass over the rows: h = a (+ b); x = h * rsqrt(mean(h^2) + eps) * gamma.
@@ -543,8 +481,8 @@ __global__ void __launch_bounds__(256) decode_prologue_kernel(const ProloguePara
       for (int j = 0; j < i; ++j) rank += (s_ids[j] == e) ? 1 : 0;    // stable: earlier flat index first
       pos = start[e] + rank;
       if (pos < p.sorted_len) p.sorted[pos] = i;
-      if (p.inv_pos) p.inv_pos[i] = pos;
     }
+    if (p.inv_pos) p.inv_pos[i] = pos;   // -1 for a rejected id: the combine skips it
     s_pos[i] = pos;
   }
   if (threadIdx.x == 0) *p.num_post = num_post;
@@ -809,8 +747,8 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
                               w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred, nullptr);
     if (rc) return rc;
     if (deferred > 1)
-      return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + 127) / 128) * 128, weights, M,
-                                      topk, dtype, residual, ld_res, out, ld_out, st);
+      return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + 127) / 128) * 128, weights,
+                                      w.inv_pos, M, topk, dtype, residual, ld_res, out, ld_out, st);
   } else {
     rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
                                w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, nullptr);
@@ -821,7 +759,7 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
     if (rc) return rc;
     if (deferred > 1)  // split-K GEMM2: its reduction, the routed weights and the sum over slots in one kernel
       return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + kTileN - 1) / kTileN) * kTileN,
-                                      weights, M, topk, dtype, residual, ld_res, out, ld_out, st);
+                                      weights, w.inv_pos, M, topk, dtype, residual, ld_res, out, ld_out, st);
   }
   if (dtype == FR_BF16)
     combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
@@ -834,27 +772,26 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
   return static_cast<int>(cudaGetLastError());
 }
 
-// Expert side of the peer-memory path: align the received rows by local expert, gather them from
-// their owners, run both GEMMs; results stay in expert-sorted order in y_sorted (memory the other
-// ranks can read) and inv_pos_out tells where each received row ended up.
-static int experts_peer_impl(const void* const* peer_x, int64_t ld_x, int world, int64_t peer_rows,
-                             const int32_t* src_rank, const int32_t* src_row, const int32_t* row_expert,
-                             const float* row_weight, const void* w1, const void* w2, int dtype, int64_t R, int H,
-                             int I, int E, void* y_sorted, int64_t y_rows, int32_t* inv_pos_out, const ExpertWs& w,
-                             cudaStream_t st) {
-  if (y_rows < w.rows) return FR_ERR_WORKSPACE;
-  int rc = align_dispatch(row_expert, R, E, kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
-                          w.num_post, nullptr, inv_pos_out, w.align_ws, w.align_ws_bytes, st);
-  if (rc) return rc;
-  permute_rows_peer_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
-      reinterpret_cast<const uint4* const*>(peer_x), ld_x / 8, world, peer_rows, src_rank, src_row, w.sorted,
-      w.num_post, R, reinterpret_cast<uint4*>(w.a_sorted), H / 8, H / 8);
-  FR_CUDA_OK(cudaGetLastError());
-  rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
-                             w.sorted, nullptr, R, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, nullptr);
-  if (rc) return rc;
-  return gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
-                               row_weight, R, y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, nullptr, nullptr);
+
+// ---- expert parallelism over peer memory (kernels in fr_ep.cu) ---------------------------------
+struct EpWs {
+  int32_t *seg_start, *seg_count, *seg_src_off, *num_post, *expert_ids, *sorted_local;
+  float* w_sorted;
+  uint16_t *a_sorted, *act;
+};
+static EpWs carve_ep(Carver& c, int64_t cap_rows, int H, int I, int E) {
+  EpWs w;
+  const size_t nseg = static_cast<size_t>(E);   // E/W local experts x W sources
+  w.seg_start = c.take<int32_t>(nseg + 1);
+  w.seg_count = c.take<int32_t>(nseg);
+  w.seg_src_off = c.take<int32_t>(nseg);
+  w.num_post = c.take<int32_t>(4);
+  w.expert_ids = c.take<int32_t>(cap_rows / kBlockM + 1);
+  w.sorted_local = c.take<int32_t>(cap_rows);
+  w.w_sorted = c.take<float>(cap_rows);
+  w.a_sorted = c.take<uint16_t>(static_cast<size_t>(cap_rows) * H);
+  w.act = c.take<uint16_t>(static_cast<size_t>(cap_rows) * I);
+  return w;
 }
 
 }  // namespace fr
@@ -982,47 +919,106 @@ int fr_permute_rows(const void* src, int dtype, int H, int64_t ld_src, const int
 
 int64_t fr_moe_experts_rows_cap(int64_t R, int E_local) { return R > 0 && E_local > 0 ? rows_cap(R, E_local) : 0; }
 
-int fr_moe_experts_peer(const void* const* peer_x, int64_t ld_x, int world, int64_t peer_rows,
-                        const int32_t* src_rank, const int32_t* src_row, const int32_t* row_expert,
-                        const float* row_weight, const void* w1, const void* w2, int dtype, int64_t R, int H, int I,
-                        int E_local, void* y_sorted, int64_t y_rows, int32_t* inv_pos_out, void* workspace,
-                        size_t workspace_bytes, void* stream) {
-  if (!peer_x || !src_rank || !src_row || !row_expert || !w1 || !w2 || !y_sorted || !inv_pos_out || R < 0 ||
-      H <= 0 || I <= 0 || E_local <= 0 || world <= 0 || peer_rows <= 0)
-    return FR_ERR_ARG;
-  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
-  if ((H % 8) || (I % 8) || (ld_x % 8)) return FR_ERR_ALIGN;
-  if (R == 0) return FR_OK;
-  if (!workspace || workspace_bytes < fr_moe_experts_workspace_bytes(R, H, I, E_local)) return FR_ERR_WORKSPACE;
-  if ((reinterpret_cast<uintptr_t>(workspace) & 1023) || (reinterpret_cast<uintptr_t>(y_sorted) & 15))
-    return FR_ERR_ALIGN;
-  Carver c(workspace);
-  void* aws;
-  size_t aws_bytes;
-  carve_align_ws(c, E_local, &aws, &aws_bytes);
-  ExpertWs ews = carve_experts(c, R, H, I, E_local);
-  ews.align_ws = aws;
-  ews.align_ws_bytes = aws_bytes;
-  return experts_peer_impl(peer_x, ld_x, world, peer_rows, src_rank, src_row, row_expert, row_weight, w1, w2, dtype,
-                           R, H, I, E_local, y_sorted, y_rows, inv_pos_out, ews, static_cast<cudaStream_t>(stream));
+size_t fr_ep_workspace_bytes(int64_t cap_rows, int H, int I, int E) {
+  if (cap_rows <= 0 || H <= 0 || I <= 0 || E <= 0) return 0;
+  Carver c(nullptr);
+  carve_ep(c, cap_rows, H, I, E);
+  return c.total();
 }
 
-int fr_combine_peer(const void* const* peer_y, int64_t ld_y, int world, int64_t peer_rows, int dtype,
-                    const int32_t* rank_of, const int32_t* pos_of, int64_t M, int topk, int H, void* out,
-                    int64_t ld_out, void* stream) {
-  if (!peer_y || !rank_of || !pos_of || !out || M < 0 || topk <= 0 || H <= 0 || world <= 0) return FR_ERR_ARG;
+int fr_ep_experts(const void* const* peer_base, int world, int rank, int64_t x_off, int64_t ld_x, int64_t peer_rows,
+                  int64_t sorted_off, int64_t tw_off, int64_t n_per_rank, int topk, const int32_t* all_counts,
+                  const void* w1, const void* w2, int dtype, int H, int I, int E, void* y_sorted, int64_t y_rows,
+                  int32_t* comb_base, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!peer_base || !all_counts || !w1 || !w2 || !y_sorted || !comb_base || world <= 0 || rank < 0 || rank >= world ||
+      peer_rows <= 0 || n_per_rank <= 0 || topk <= 0 || H <= 0 || I <= 0 || E <= 0 || y_rows <= 0)
+    return FR_ERR_ARG;
+  if (E % world || E > kEpMaxExperts) return FR_ERR_UNSUPPORTED;
   if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
-  if ((H % 8) || (ld_y % 8) || (ld_out % 8) || (reinterpret_cast<uintptr_t>(out) & 15)) return FR_ERR_ALIGN;
+  if ((H % 8) || (I % 8) || (ld_x % 8) || (x_off % 16) || (sorted_off % 4) || (tw_off % 4) || (y_rows % kBlockM) ||
+      (reinterpret_cast<uintptr_t>(y_sorted) & 15))
+    return FR_ERR_ALIGN;
+  if (y_rows >= (int64_t(1) << 31)) return FR_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < fr_ep_workspace_bytes(y_rows, H, I, E)) return FR_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(workspace) & 1023) return FR_ERR_ALIGN;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int El = E / world;
+  Carver c(workspace);
+  EpWs w = carve_ep(c, y_rows, H, I, E);
+
+  EpPlanParams pp = {};
+  pp.counts = all_counts;
+  pp.W = world;
+  pp.E = E;
+  pp.El = El;
+  pp.rank = rank;
+  pp.cap_rows = y_rows;
+  pp.seg_start = w.seg_start;
+  pp.seg_count = w.seg_count;
+  pp.seg_src_off = w.seg_src_off;
+  pp.comb_base = comb_base;
+  pp.num_post = w.num_post;
+  pp.expert_ids = w.expert_ids;
+  ep_plan_kernel<<<1, 256, 0, st>>>(pp);
+  FR_CUDA_OK(cudaGetLastError());
+
+  EpGatherParams gp = {};
+  gp.peer_base = reinterpret_cast<const uint8_t* const*>(peer_base);
+  gp.x_off = x_off;
+  gp.sorted_off = sorted_off;
+  gp.tw_off = tw_off;
+  gp.ld_x_v = ld_x / 8;
+  gp.peer_rows = peer_rows;
+  gp.n_per_rank = n_per_rank;
+  gp.W = world;
+  gp.El = El;
+  gp.topk = topk;
+  gp.row_v = H / 8;
+  gp.seg_start = w.seg_start;
+  gp.seg_count = w.seg_count;
+  gp.seg_src_off = w.seg_src_off;
+  gp.num_post = w.num_post;
+  gp.a_sorted = reinterpret_cast<uint4*>(w.a_sorted);
+  gp.ld_a_v = H / 8;
+  gp.w_sorted = w.w_sorted;
+  gp.sorted_local = w.sorted_local;
+  gp.cap_rows = y_rows;
+  const int64_t want = static_cast<int64_t>(sm_count_or_default()) * 16;
+  const unsigned ggrid = static_cast<unsigned>(y_rows < want ? y_rows : want);
+  ep_gather_kernel<<<ggrid, 256, (static_cast<size_t>(E) + 1) * sizeof(int), st>>>(gp);
+  FR_CUDA_OK(cudaGetLastError());
+
+  // Both GEMMs on the rows in use (the count lives on the device; tiles beyond it are never started).  The row
+  // count the tile order is tuned for is the balanced share, n_per_rank.  No split-K: its scratch is sized by rows.
+  int rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, y_rows, H, I, El, 2 * I, w.expert_ids, w.num_post,
+                                 w.sorted_local, nullptr, y_rows, w.act, I, 1, nullptr, 0, st, nullptr, nullptr,
+                                 n_per_rank);
+  if (rc) return rc;
+  return gemm_grouped_dispatch(1, w.act, I, w2, dtype, y_rows, I, H, El, H, w.expert_ids, w.num_post, w.sorted_local,
+                               w.w_sorted, y_rows, y_sorted, H, 1, nullptr, 0, st, nullptr, nullptr, n_per_rank);
+}
+
+int fr_ep_combine(const void* const* peer_base, int world, int64_t y_off, int64_t ld_y, int64_t y_rows, int dtype,
+                  const int32_t* topk_ids, const int32_t* inv_pos, const int32_t* comb_base, int64_t M, int topk, int H,
+                  int E, void* out, int64_t ld_out, void* stream) {
+  if (!peer_base || !topk_ids || !inv_pos || !comb_base || !out || M < 0 || topk <= 0 || H <= 0 || world <= 0 ||
+      E <= 0 || y_rows <= 0)
+    return FR_ERR_ARG;
+  if (E % world) return FR_ERR_UNSUPPORTED;
+  if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
+  if ((H % 8) || (ld_y % 8) || (ld_out % 8) || (y_off % 16) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return FR_ERR_ALIGN;
   if (M == 0) return FR_OK;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const uint8_t* const* pb = reinterpret_cast<const uint8_t* const*>(peer_base);
   if (dtype == FR_BF16)
-    combine_peer_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(
-        reinterpret_cast<const uint4* const*>(peer_y), ld_y / 8, world, peer_rows, rank_of, pos_of, topk, H / 8,
-        static_cast<uint4*>(out), ld_out / 8);
+    ep_combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(pb, y_off, ld_y / 8, y_rows, world, E / world, E,
+                                                                      topk_ids, inv_pos, comb_base, topk, H / 8,
+                                                                      static_cast<uint4*>(out), ld_out / 8);
   else
-    combine_peer_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(
-        reinterpret_cast<const uint4* const*>(peer_y), ld_y / 8, world, peer_rows, rank_of, pos_of, topk, H / 8,
-        static_cast<uint4*>(out), ld_out / 8);
+    ep_combine_kernel<false><<<static_cast<unsigned>(M), 256, 0, st>>>(pb, y_off, ld_y / 8, y_rows, world, E / world,
+                                                                       E, topk_ids, inv_pos, comb_base, topk, H / 8,
+                                                                       static_cast<uint4*>(out), ld_out / 8);
   return static_cast<int>(cudaGetLastError());
 }
 
@@ -1320,7 +1316,8 @@ int fr_moe_layer_fp8(const void* x, const void* gate, int64_t gate_stride_h, int
     partial_cols = static_cast<int64_t>((H + kTileN - 1) / kTileN) * kTileN;
   }
   if (deferred > 1)
-    return combine_partial_dispatch(w.split, deferred, n, H, partial_cols, tw, M, topk, dtype, nullptr, 0, out, H, st);
+    return combine_partial_dispatch(w.split, deferred, n, H, partial_cols, tw, w.inv_pos, M, topk, dtype, nullptr, 0, out,
+                                    H, st);
   if (bf)
     combine_kernel<true><<<static_cast<unsigned>(M), 256, 0, st>>>(reinterpret_cast<const uint4*>(w.y_sorted), H / 8,
                                                                    w.inv_pos, topk, H / 8, w.rows, nullptr, 0,

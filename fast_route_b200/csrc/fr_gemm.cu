@@ -240,7 +240,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld32(taddr + HALF + c0, u);
           tc_wait_ld();
           uint32_t pk[16];
-#pragma unroll
           const int col = nb * HALF + c0;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -273,7 +272,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tmem_ld32(taddr + c0, a);
           tc_wait_ld();
           uint32_t pk[16];
-#pragma unroll
           const int col = nb * BN + c0;
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
@@ -393,8 +391,9 @@ splitk_reduce_weighted_kernel(const float* __restrict__ partial, int64_t partial
 template <bool BF16>
 __global__ void __launch_bounds__(256)
 combine_partial_kernel(const float* __restrict__ partial, int64_t partial_cols, int split_k, int64_t n_valid,
-                       const float* __restrict__ topk_w, int topk, int H, const uint16_t* __restrict__ residual,
-                       int64_t ld_res, uint16_t* __restrict__ out, int64_t ld_out) {
+                       const float* __restrict__ topk_w, const int32_t* __restrict__ inv_pos, int topk, int H,
+                       const uint16_t* __restrict__ residual, int64_t ld_res, uint16_t* __restrict__ out,
+                       int64_t ld_out) {
   const int64_t t = blockIdx.y;
   const int j = (blockIdx.x * 256 + threadIdx.x) * 4;
   if (j >= H) return;
@@ -406,6 +405,7 @@ combine_partial_kernel(const float* __restrict__ partial, int64_t partial_cols, 
   }
   for (int q = 0; q < topk; ++q) {
     const int64_t sid = t * topk + q;
+    if (inv_pos && __ldg(inv_pos + sid) < 0) continue;   // assignment rejected by the align stage: no partial rows
     const float w = topk_w ? __ldg(topk_w + sid) : 1.0f;
     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < split_k; ++s) {
@@ -510,7 +510,7 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st, int* deferred_split, const QuantArgs* quant) {
+                          cudaStream_t st, int* deferred_split, const QuantArgs* quant, int64_t rows_hint = -1) {
   // quant != nullptr: a and w hold E4M3 bytes (lda and K count elements = bytes), dtype is the output type.
   // which: 0 = GEMM1 (two-box B, SiLU epilogue), 1 = GEMM2 (weighted epilogue).
   // deferred_split (GEMM2 only, may be null): when split-K is used, skip the reduction and
@@ -556,7 +556,8 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
   // A group's A rows stay in L2 while its B tiles stream through; with ~32 row blocks per
   // expert a group of 32 lets each expert's weights be fetched from HBM once instead of twice,
   // with few blocks per expert a wider group only spreads the in-flight tiles over more experts.
-  const int64_t blocks_per_expert = n_valid / (static_cast<int64_t>(BM) * E);
+  // rows_hint: the expected number of real rows when n_valid is only a capacity (expert-parallel callers)
+  const int64_t blocks_per_expert = (rows_hint >= 0 ? rows_hint : n_valid) / (static_cast<int64_t>(BM) * E);
   p.group_m = blocks_per_expert >= 24 ? (which == 0 ? 32 : 24) : 16;
   p.partial_cols = static_cast<int64_t>(p.num_nb) * GEMM_BN;
   if (split_k > 1) {
@@ -626,17 +627,17 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
 }
 
 int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, int64_t partial_cols,
-                             const float* topk_w, int64_t M, int topk, int dtype, const void* residual,
-                             int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st) {
+                             const float* topk_w, const int32_t* inv_pos, int64_t M, int topk, int dtype,
+                             const void* residual, int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st) {
   const dim3 grid(static_cast<unsigned>((n_out + 1023) / 1024), static_cast<unsigned>(M));
   if (dtype == FR_BF16)
     combine_partial_kernel<true><<<grid, 256, 0, st>>>(static_cast<const float*>(workspace), partial_cols, split_k,
-                                                       n_valid, topk_w, topk, n_out,
+                                                       n_valid, topk_w, inv_pos, topk, n_out,
                                                        static_cast<const uint16_t*>(residual), ld_res,
                                                        static_cast<uint16_t*>(out), ld_out);
   else
     combine_partial_kernel<false><<<grid, 256, 0, st>>>(static_cast<const float*>(workspace), partial_cols, split_k,
-                                                        n_valid, topk_w, topk, n_out,
+                                                        n_valid, topk_w, inv_pos, topk, n_out,
                                                         static_cast<const uint16_t*>(residual), ld_res,
                                                         static_cast<uint16_t*>(out), ld_out);
   return static_cast<int>(cudaGetLastError());

@@ -206,7 +206,22 @@ tokenn_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       TileInfo t;
       decode(tile, e_ptr, t);
       const uint32_t buf = it & 1u, aphase = (it >> 1) & 1u;
-      if (!wait_or_abort(&tfull[buf], aphase, abort_flag, 0x603)) break;
+      // The four epilogue warps share the staging tile and meet at a named barrier in every chunk, so they must
+      // all take the same decision here: a vote over the 128 threads (every warp reaches it, its wait is bounded).
+      const uint32_t got = wait_or_abort(&tfull[buf], aphase, abort_flag, 0x603) ? 1u : 0u;
+      __syncwarp();
+      uint32_t all_got;
+      asm volatile(
+          "{\n"
+          ".reg .pred p, q;\n"
+          "setp.ne.u32 p, %1, 0;\n"
+          "bar.red.and.pred q, 1, 128, p;\n"
+          "selp.u32 %0, 1, 0, q;\n"
+          "}\n"
+          : "=r"(all_got)
+          : "r"(got)
+          : "memory");
+      if (!all_got) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * TN_MAX;
       const int nchunks = (t.tn + 31) / 32;

@@ -564,6 +564,8 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
       if (lane == (__ffs(grp) - 1)) my[e] += __popc(grp);
       if (pos < p.sorted_len) p.sorted[pos] = static_cast<int32_t>(i);
       if (p.inv_pos) p.inv_pos[i] = pos;
+    } else if (i < hi && p.inv_pos) {
+      p.inv_pos[i] = -1;   // rejected id: the combine must not pick up a stale position
     }
     __syncwarp();
   };
@@ -616,7 +618,10 @@ int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* s
   {
     const int rc = align_coop_dispatch(topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len,
                                        num_post, counts, inv_pos, workspace, workspace_bytes, st);
-    if (rc != FR_ERR_UNSUPPORTED) return rc;
+    if (rc <= 0 && rc != FR_ERR_UNSUPPORTED) return rc;
+    // a launch the device refused (cooperative grid too large for a partitioned GPU, ...) is not
+    // fatal: clear the error and let the cluster kernel take the call
+    if (rc > 0) (void)cudaGetLastError();
   }
 
   int threads = 1024;

@@ -6,6 +6,8 @@
 // moe_align_block_size, ops/fused_moe.py:133-175).
 #include <cooperative_groups.h>
 
+#include <atomic>
+
 #include "fr_common.cuh"
 
 namespace fr {
@@ -209,6 +211,8 @@ template int launch_topk16<__nv_bfloat16>(const void*, int64_t, int, int64_t, in
 // bar[0] = arrival count, bar[1] = generation; both start at zero and the count is zero
 // again after every completed barrier.  If the wait runs out the status block records it
 // and every block leaves the kernel; the two words must then be cleared before reuse.
+// bar[3] = how many polls a block may spend waiting (0 = the default, about a second); a
+// caller that wants a shorter limit writes it there, next to the barrier words it owns.
 __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int nblocks) {
   __shared__ int ok_flag;
   __syncthreads();
@@ -223,9 +227,11 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int nbl
       __threadfence();
       atomicAdd(bar + 1, 1u);
     } else {
+      const unsigned int asked = __ldcg(bar + 3);
+      const uint32_t budget = asked ? asked : (1u << 22);
       uint32_t it = 0;
       while (*vgen == gen) {
-        if (++it > (1u << 22)) {
+        if (++it > budget) {
           ok = 0;
           report(ST_WAIT_TIMEOUT, 0x500);
           break;
@@ -369,6 +375,8 @@ __global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
       const int64_t flat = lo_blk + i;
       if (pos < p.sorted_len) p.sorted[pos] = static_cast<int32_t>(flat);
       if (p.inv_pos) p.inv_pos[flat] = pos;
+    } else if (i < whi && p.inv_pos) {
+      p.inv_pos[lo_blk + i] = -1;   // rejected id: the combine must not pick up a stale position
     }
     __syncwarp();
   }
@@ -464,24 +472,30 @@ constexpr int kNoAllocMaxExperts = FR_ALIGN_NOALLOC_MAX_EXPERTS;
 constexpr size_t kNoAllocScratchBytes = 256 + static_cast<size_t>(256) * kNoAllocMaxExperts * sizeof(int32_t);
 
 // Barrier words + per-block histograms for up to kNoAllocMaxExperts experts.  Every GPU that
-// loads the library holds these 257 KB until the process exits.
+// loads the library holds these 262,400 bytes (256.25 KB) until the process exits.
 static __device__ __align__(256) unsigned char g_align_noalloc_scratch[kNoAllocScratchBytes];
 
 // In host code the array's name is only a handle; the device address comes from
-// cudaGetSymbolAddress, looked up once per device with that device current.
-static int noalloc_scratch_ptr(void** out) {
+// cudaGetSymbolAddress, looked up once per device with that device current.  The table is
+// read and filled from any host thread (two threads that race on the first call both store
+// the same address).  The look-up is refused while the stream is being captured: the first
+// call on a device belongs before any capture.
+static int noalloc_scratch_ptr(void** out, cudaStream_t st) {
   constexpr int kMaxDevices = 64;
-  static void* cached[kMaxDevices] = {};
+  static std::atomic<void*> cached[kMaxDevices];
   int dev = 0;
   FR_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return FR_ERR_UNSUPPORTED;
-  if (!cached[dev]) {
-    void* ptr = nullptr;
+  void* ptr = cached[dev].load(std::memory_order_acquire);
+  if (!ptr) {
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    FR_CUDA_OK(cudaStreamIsCapturing(st, &cap));
+    if (cap != cudaStreamCaptureStatusNone) return FR_ERR_UNSUPPORTED;
     FR_CUDA_OK(cudaGetSymbolAddress(&ptr, g_align_noalloc_scratch));
     if (!ptr) return FR_ERR_DRIVER;
-    cached[dev] = ptr;
+    cached[dev].store(ptr, std::memory_order_release);
   }
-  *out = cached[dev];
+  *out = ptr;
   return FR_OK;
 }
 
@@ -495,11 +509,12 @@ int align_noalloc_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, in
   if (sorted_len < n + static_cast<int64_t>(E) * (bs - 1)) return FR_ERR_ARG;
   if (expert_ids_len < (n + static_cast<int64_t>(E) * (bs - 1)) / bs) return FR_ERR_ARG;
   void* scratch = nullptr;
-  const int rc = noalloc_scratch_ptr(&scratch);
+  const int rc = noalloc_scratch_ptr(&scratch, st);
   if (rc) return rc;
-  // The array keeps whatever the previous call left.  Only the two barrier words must start
-  // at zero (a call that ended in a reported timeout could have left a count behind); the
-  // histogram rows are fully rewritten before they are read.
+  // The array keeps whatever the previous call left.  Only its first 16 bytes must start at
+  // zero: the two barrier words (a call that ended in a reported timeout could have left a
+  // count behind) and the wait-budget word; the histogram rows are fully rewritten before
+  // they are read.
   FR_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
   return align_coop_dispatch(topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post,
                              counts, inv_pos, scratch, kNoAllocScratchBytes, st, /*min_n=*/1);

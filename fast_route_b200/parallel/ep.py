@@ -180,108 +180,253 @@ def fused_moe_ep(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: torc
 
 
 # ------------------------------------------------------------------------------------
-# the layer over peer memory: dispatch fused into the gather, return fused into the combine
+# the layer over peer memory: dispatch fused into the gather, return fused into the combine,
+# no sizes on the host
 # ------------------------------------------------------------------------------------
-class PeerBuffers:
-    """Symmetric (peer-readable) staging memory of one rank: ``x[rows, H]`` holds this rank's
-    tokens, ``y[y_rows, H]`` its experts' results in expert-sorted order.  Allocation and the
-    rendezvous are collective: every rank must construct it with the same arguments."""
+BLOCK_M = 128
 
-    def __init__(self, group: ExpertParallelGroup, rows: int, H: int, topk: int, dtype, device):
-        import torch.distributed._symmetric_memory as symm_mem
+
+def plan_tables(all_counts, rank: int, block: int = BLOCK_M):
+    """Host mirror (numpy) of the device plan of ``fr_ep_experts``: from ``all_counts[W][E]`` (tokens of rank s
+    for expert e) the tables of rank ``rank``.  Returns a dict with
+
+    * ``seg_start[El*W+1]``, ``seg_count[El*W]``, ``seg_src_off[El*W]`` - as expert owner: segment (j, s) = the rows
+      of source rank s for local expert j; first row in the expert-sorted operand (experts padded to ``block`` rows,
+      sources in rank order inside an expert), length, and first entry in source s's expert-sorted list;
+    * ``num_post`` - rows of the operand in use; ``expert_ids[num_post/block]``;
+    * ``comb_base[E]`` - as token owner: this rank's assignment at position q of its own sorted list, going to
+      expert e, lands in row ``comb_base[e] + q`` of the y buffer of rank ``e // El``.
+
+    Used by the CPU-rank tests and to check the kernel; the GPU path never calls it."""
+    import numpy as np
+    c = np.maximum(np.asarray(all_counts, dtype=np.int64), 0)
+    W, E = c.shape
+    El = E // W
+    tot = c.sum(0)
+    padded = (tot + block - 1) // block * block
+    start = np.zeros(E, dtype=np.int64)
+    for o in range(W):
+        start[o * El:(o + 1) * El] = np.concatenate([[0], np.cumsum(padded[o * El:(o + 1) * El])[:-1]])
+    below = c[:rank].sum(0)
+    selfpre = np.concatenate([[0], np.cumsum(c[rank])[:-1]])
+    lo = rank * El
+    num_post = int(padded[lo:lo + El].sum())
+    seg_start = np.zeros(El * W + 1, dtype=np.int64)
+    seg_count = np.zeros(El * W, dtype=np.int64)
+    seg_src_off = np.zeros(El * W, dtype=np.int64)
+    for j in range(El):
+        for s_ in range(W):
+            i = j * W + s_
+            seg_start[i] = start[lo + j] + c[:s_, lo + j].sum()
+            seg_count[i] = c[s_, lo + j]
+            seg_src_off[i] = c[s_, :lo + j].sum()
+    seg_start[El * W] = num_post
+    expert_ids = np.repeat(np.arange(El), padded[lo:lo + El] // block)
+    return {"seg_start": seg_start, "seg_count": seg_count, "seg_src_off": seg_src_off, "num_post": num_post,
+            "expert_ids": expert_ids, "comb_base": start + below - selfpre}
+
+
+def _round_up(a: int, b: int) -> int:
+    return (a + b - 1) // b * b
+
+
+class PeerRegion:
+    """The peer-readable memory of one rank, one allocation with the same layout on every rank:
+    ``x[rows,H]`` its tokens, ``y[y_rows,H]`` the results of its own experts in expert-sorted order,
+    ``sorted[n]`` its assignments ordered by expert, ``tw[n]`` its routing weights (n = rows * topk).
+    ``base_ptrs`` is the device address of the table of every rank's region base.
+
+    ``PeerRegion(group, ...)`` allocates symmetric memory and is collective (every rank, same arguments).
+    ``PeerRegion.emulated(world, ...)`` builds ``world`` regions in ordinary memory of ONE GPU that share a pointer
+    table: the same kernels then run rank after rank in one process (tests on a single-GPU box)."""
+
+    def __init__(self, group: ExpertParallelGroup, rows: int, H: int, topk: int, dtype, device, _buf=None,
+                 _table=None, _world=None, _experts_per_rank=None):
         from .. import _lib
-        self.group, self.rows, self.H, self.topk, self.dtype = group, rows, H, topk, dtype
         lib = _lib.load()
+        world = group.world if group is not None else _world
+        epr = group.experts_per_rank if group is not None else _experts_per_rank
+        self.group, self.rows, self.H, self.topk, self.dtype, self.world = group, rows, H, topk, dtype, world
+        self.n = rows * topk
+        esz = torch.empty(0, dtype=dtype).element_size()
         # worst case: every assignment of every rank lands on this rank
-        self.y_rows = int(lib.fr_moe_experts_rows_cap(rows * topk * group.world, group.experts_per_rank))
-        self.x = symm_mem.empty((rows, H), dtype=dtype, device=device)
-        self.y = symm_mem.empty((self.y_rows, H), dtype=dtype, device=device)
-        self.hx = symm_mem.rendezvous(self.x, group.pg)
-        self.hy = symm_mem.rendezvous(self.y, group.pg)
-        self.x_ptrs = self.hx.buffer_ptrs_dev      # device address of the table of per-rank base pointers
-        self.y_ptrs = self.hy.buffer_ptrs_dev
+        self.y_rows = int(lib.fr_moe_experts_rows_cap(self.n * world, epr))
+        self.x_off = 0
+        self.y_off = _round_up(rows * H * esz, 1024)
+        self.sorted_off = self.y_off + _round_up(self.y_rows * H * esz, 1024)
+        self.tw_off = self.sorted_off + _round_up(self.n * 4, 1024)
+        self.nbytes = self.tw_off + _round_up(self.n * 4, 1024)
+        if _buf is None:
+            import os
+            # symmetric memory would otherwise bind the buffers to an NVLink multicast object, which nothing here
+            # uses (peer memory is only read by plain loads) and which must not outlive a rank that dies
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buf = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self.handle = symm_mem.rendezvous(self.buf, group.pg)
+            self.base_ptrs = int(self.handle.buffer_ptrs_dev)
+        else:
+            self.buf, self.handle, self.base_ptrs = _buf, None, int(_table.data_ptr())
+            self._table = _table
+        b = self.buf
+        self.x = b[self.x_off:self.x_off + rows * H * esz].view(dtype).view(rows, H)
+        self.y = b[self.y_off:self.y_off + self.y_rows * H * esz].view(dtype).view(self.y_rows, H)
+        self.sorted = b[self.sorted_off:self.sorted_off + self.n * 4].view(torch.int32)
+        self.tw = b[self.tw_off:self.tw_off + self.n * 4].view(torch.float32)
+        self.comb_base = None
+        self.sync_word = torch.zeros(1, dtype=torch.int32, device=device)
+
+    @classmethod
+    def emulated(cls, world: int, num_experts: int, rows: int, H: int, topk: int, dtype, device):
+        from .. import _lib
+        epr = num_experts // world
+        esz = torch.empty(0, dtype=dtype).element_size()
+        n = rows * topk
+        y_rows = int(_lib.load().fr_moe_experts_rows_cap(n * world, epr))
+        nbytes = _round_up(rows * H * esz, 1024) + _round_up(y_rows * H * esz, 1024) + 2 * _round_up(n * 4, 1024)
+        table = torch.zeros(world, dtype=torch.int64, device=device)
+        regions = []
+        for r in range(world):
+            buf = torch.zeros(nbytes + 1024, dtype=torch.uint8, device=device)
+            off = (-buf.data_ptr()) % 1024
+            buf = buf[off:off + nbytes]
+            table[r] = buf.data_ptr()
+            regions.append(cls(None, rows, H, topk, dtype, device, _buf=buf, _table=table, _world=world,
+                               _experts_per_rank=epr))
+        return regions
+
+
+class RouteState:
+    """What a rank keeps between the stages of one call."""
+    __slots__ = ("M", "ids", "inv_pos", "counts")
+
+
+def ep_route_stage(region: PeerRegion, hidden_states: torch.Tensor, gate: torch.Tensor, topk: int,
+                   num_experts: int, renormalize: bool = True) -> RouteState:
+    """Stage 1 (local): tokens into the region, fused router with the weights written straight into the region,
+    align with block size 1 whose sorted list lands in the region.  Returns ids, positions and the histogram."""
+    from .. import _lib
+    lib = _lib.load()
+    dev = hidden_states.device
+    M, H = hidden_states.shape
+    E = num_experts
+    assert M <= region.rows and H == region.H and topk == region.topk and hidden_states.dtype == region.dtype
+    n = M * topk
+    dt = _lib.dtype_code(hidden_states.dtype)
+    region.x[:M].copy_(hidden_states)
+    st = RouteState()
+    st.M = M
+    st.ids = torch.empty(M, topk, dtype=torch.int32, device=dev)
+    st.inv_pos = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
+    st.counts = torch.empty(E, dtype=torch.int32, device=dev)
+    ws = _lib.workspace(lib.fr_route_fused_workspace_bytes(M, H, E, topk), dev, "route")
+    rc = lib.fr_route_fused(_lib.ptr(region.x), dt, M, H, region.x.stride(0), _lib.ptr(gate), gate.stride(0),
+                            gate.stride(1), E, topk, 1 if renormalize else 0, _lib.ptr(region.tw), _lib.ptr(st.ids),
+                            None, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+    _lib.check(rc, "fr_route_fused")
+    expert_of_row = _lib.workspace(4 * max(n, 1), dev, "ep_block1")      # block size 1: one entry per assignment
+    num_post = torch.empty(1, dtype=torch.int32, device=dev)
+    aws = _lib.workspace(lib.fr_align_workspace_bytes(E), dev, "align")
+    rc = lib.fr_align(_lib.ptr(st.ids), n, E, 1, _lib.ptr(region.sorted), n, _lib.ptr(expert_of_row), n,
+                      _lib.ptr(num_post), _lib.ptr(st.counts), _lib.ptr(st.inv_pos), _lib.ptr(aws), aws.numel(),
+                      _lib.stream_ptr(dev))
+    _lib.check(rc, "fr_align")
+    return st
+
+
+def ep_experts_stage(region: PeerRegion, rank: int, all_counts: torch.Tensor, w1_local: torch.Tensor,
+                     w2_local: torch.Tensor, num_experts: int, rows_hint: int = None) -> None:
+    """Stage 2 (after every rank's stage 1 is visible): plan from the gathered histograms, gather of the token rows
+    from their owners, both grouped GEMMs; results stay in ``region.y``."""
+    from .. import _lib
+    lib = _lib.load()
+    dev = w1_local.device
+    El, N2, H = w1_local.shape
+    I = N2 // 2
+    assert all_counts.dtype == torch.int32 and all_counts.is_contiguous()
+    assert all_counts.shape == (region.world, num_experts) and El * region.world == num_experts
+    if region.comb_base is None:
+        region.comb_base = torch.empty(num_experts, dtype=torch.int32, device=dev)
+    ws = _lib.workspace(lib.fr_ep_workspace_bytes(region.y_rows, H, I, num_experts), dev, "ep_experts")
+    rc = lib.fr_ep_experts(ctypes_ptr(region.base_ptrs), region.world, rank, region.x_off, region.x.stride(0),
+                           region.rows, region.sorted_off, region.tw_off, region.n, region.topk,
+                           _lib.ptr(all_counts), _lib.ptr(w1_local), _lib.ptr(w2_local),
+                           _lib.dtype_code(region.dtype), H, I, num_experts, _lib.ptr(region.y), region.y_rows,
+                           _lib.ptr(region.comb_base), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+    _lib.check(rc, "fr_ep_experts")
+
+
+def ep_combine_stage(region: PeerRegion, st: RouteState, num_experts: int, out: torch.Tensor = None) -> torch.Tensor:
+    """Stage 3 (after every rank's stage 2 is visible): each token's k result rows summed straight out of the
+    expert owners' memory."""
+    from .. import _lib
+    lib = _lib.load()
+    dev = st.ids.device
+    if out is None:
+        out = torch.empty(st.M, region.H, dtype=region.dtype, device=dev)
+    rc = lib.fr_ep_combine(ctypes_ptr(region.base_ptrs), region.world, region.y_off, region.y.stride(0), region.y_rows,
+                           _lib.dtype_code(region.dtype), _lib.ptr(st.ids), _lib.ptr(st.inv_pos),
+                           _lib.ptr(region.comb_base), st.M, region.topk, region.H, num_experts, _lib.ptr(out),
+                           out.stride(0), _lib.stream_ptr(dev))
+    _lib.check(rc, "fr_ep_combine")
+    return out
 
 
 _peer_state: dict = {}
 
 
-def _peer_buffers(group, M, H, topk, dtype, device) -> PeerBuffers:
+def _peer_region(group, M, H, topk, dtype, device) -> PeerRegion:
     key = (id(group.pg), H, topk, dtype, device.index)
-    pb = _peer_state.get(key)
-    if pb is None or pb.rows < M:
-        pb = PeerBuffers(group, M, H, topk, dtype, device)
-        _peer_state[key] = pb
-    return pb
+    pr = _peer_state.get(key)
+    if pr is None or pr.rows < M:
+        pr = PeerRegion(group, M, H, topk, dtype, device)
+        _peer_state[key] = pr
+    return pr
 
 
 def fused_moe_ep_p2p(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: torch.Tensor,
                      w2_local: torch.Tensor, topk: int, group: ExpertParallelGroup,
-                     renormalize: bool = True) -> torch.Tensor:
-    """Expert-parallel MoE layer in which token rows cross NVLink exactly once each way and are
-    never packed into send / receive buffers:
+                     renormalize: bool = True, timers=None) -> torch.Tensor:
+    """Expert-parallel MoE layer in which token rows cross NVLink exactly once each way, are never packed into
+    send / receive buffers, and no size ever reaches the host (no synchronisation, no allocation that depends on
+    the routing):
 
-    * only 8 bytes of metadata per assignment (token index, routing weight) travel through an
-      NCCL all-to-all; the expert owner's gather kernel then reads the token rows directly from
+    * the only metadata that travels is one all-gather of the per-expert histograms (E integers per rank);
+      every rank derives from it, on the device, where each (expert, source rank) segment sits in the owner's
+      operand and where each of its own assignments will be found in the owner's results;
+    * the expert owner's gather kernel reads the token rows (and their 8 bytes of routing data) directly from
       the memory of the GPUs that hold them while it builds the expert-sorted GEMM operand;
-    * the results stay on the expert owner; 4 bytes per assignment (its row in that buffer) go
-      back, and the source's combine kernel sums the k result rows of each token straight out
-      of the owners' memory.
+    * the results stay on the expert owner; the source's combine kernel sums the k result rows of each token
+      straight out of the owners' memory.
 
-    The two small all-to-alls also order the ranks: a peer's tokens are complete before anyone
-    gathers them, a peer's results before anyone combines them, and nobody overwrites a buffer
-    a peer may still be reading.  Every rank must call with the same M (rows per rank).
-    """
-    from .. import _lib
-    from ..ops import fused_moe as fm
-    from ..ops.stable_route import fused_route
-
-    lib = _lib.load()
+    The all-gather and one more tiny collective order the ranks: a peer's tokens and routing are complete
+    before anyone gathers them, a peer's results before anyone combines them, and nobody overwrites a region a
+    peer may still be reading (a rank reaches the next call's writes only after it has passed the collective
+    that every reader entered after its reads).  ``timers`` (a list) receives (name, start, end) CUDA events of
+    the stages.  Every rank must call with at most ``rows`` tokens of the region it first allocated (the first
+    call's M; larger batches re-allocate collectively, so all ranks must grow together)."""
     dev = hidden_states.device
     M, H = hidden_states.shape
-    El, N2, _ = w1_local.shape
-    I = N2 // 2
     E, W = group.num_experts, group.world
-    assert El == group.experts_per_rank and gate.shape == (H, E)
-    n = M * topk
-    dt = _lib.dtype_code(hidden_states.dtype)
-    pb = _peer_buffers(group, M, H, topk, hidden_states.dtype, dev)
-    pb.x[:M].copy_(hidden_states)
+    assert w1_local.shape[0] == group.experts_per_rank and gate.shape == (H, E)
+    region = _peer_region(group, M, H, topk, hidden_states.dtype, dev)
 
-    tw, ti = fused_route(hidden_states, gate, topk, renormalize=renormalize)
-    sorted_ids, _, _, counts, inv_pos = fm.moe_align_block_size(ti, 1, E, return_extra=True)
-    recv_counts = exchange_counts(counts, group)
-    counts_h, recv_h = counts.cpu(), recv_counts.cpu()              # the one host sync: split sizes
-    validate_counts(counts_h, n, recv_h)
-    in_splits = send_splits(counts_h, W)
-    out_splits = recv_h.sum(dim=1).tolist()
+    def mark(name, fn):
+        if timers is None:
+            return fn()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        r = fn()
+        b.record()
+        timers.append((name, a, b))
+        return r
 
-    # metadata in destination order: (token row on this rank, routing weight bits)
-    order = sorted_ids[:n].long()
-    meta = torch.stack([(order // topk).to(torch.int32), tw.reshape(-1)[order].view(torch.int32)], dim=1)
-    recv_meta = all_to_all_rows(meta, in_splits, out_splits, group)
-    R = recv_meta.shape[0]
-    inv_out = torch.empty(max(R, 1), dtype=torch.int32, device=dev)
-    if R:
-        src_rank = torch.repeat_interleave(torch.arange(W, dtype=torch.int32, device=dev),
-                                           recv_counts.sum(dim=1), output_size=R)
-        src_row = recv_meta[:, 0].contiguous()
-        row_w = recv_meta[:, 1].contiguous().view(torch.float32)
-        row_expert = recv_row_experts(recv_counts, R)
-        nbytes = lib.fr_moe_experts_workspace_bytes(R, H, I, El)
-        ws = _lib.workspace(nbytes, dev, "ep_experts")
-        rc = lib.fr_moe_experts_peer(ctypes_ptr(pb.x_ptrs), H, W, pb.rows, _lib.ptr(src_rank), _lib.ptr(src_row),
-                                     _lib.ptr(row_expert), _lib.ptr(row_w), _lib.ptr(w1_local), _lib.ptr(w2_local),
-                                     dt, R, H, I, El, _lib.ptr(pb.y), pb.y_rows, _lib.ptr(inv_out), _lib.ptr(ws),
-                                     ws.numel(), _lib.stream_ptr(dev))
-        _lib.check(rc, "fr_moe_experts_peer")
-    back_pos = all_to_all_rows(inv_out[:R], out_splits, in_splits, group)      # in this rank's sorted order
-    pos_of = back_pos[inv_pos.long()].contiguous()
-    rank_of = (ti.reshape(-1) // group.experts_per_rank).to(torch.int32).contiguous()
-    out = torch.empty_like(hidden_states)
-    rc = lib.fr_combine_peer(ctypes_ptr(pb.y_ptrs), H, W, pb.y_rows, dt, _lib.ptr(rank_of), _lib.ptr(pos_of), M, topk,
-                             H, _lib.ptr(out), H, _lib.stream_ptr(dev))
-    _lib.check(rc, "fr_combine_peer")
-    return out
+    st = mark("route+align", lambda: ep_route_stage(region, hidden_states, gate, topk, E, renormalize))
+    all_counts = torch.empty(W, E, dtype=torch.int32, device=dev)
+    mark("count all-gather", lambda: dist.all_gather_into_tensor(all_counts.view(-1), st.counts, group=group.pg))
+    mark("gather+experts", lambda: ep_experts_stage(region, group.rank, all_counts, w1_local, w2_local, E))
+    mark("results-ready sync", lambda: dist.all_reduce(region.sync_word, group=group.pg))
+    return mark("combine", lambda: ep_combine_stage(region, st, E))
 
 
 def ctypes_ptr(addr: int):

@@ -44,7 +44,7 @@ const char* fr_error_string(int code);
 
 /* Synchronous read (and clear) of the device status block of the current device:
  * out4[0] = first error code (0 ok, 1 wait timeout, 2 expert id out of range,
- * 3 bad sorted id), out4[1] = detail, out4[2] = block, out4[3] = count.
+ * 3 bad sorted id, 4 expert-parallel receive capacity exceeded), out4[1] = detail, out4[2] = block, out4[3] = count.
  * No counterpart in the reference, whose kernels have no error reporting. */
 int fr_check_status(unsigned int* out4);
 
@@ -75,12 +75,15 @@ int fr_softmax_topk(const void* logits, int dtype, int64_t M, int E, int64_t str
  * op it calls plus the fill_ of the wrapper).  sorted_ids has sorted_len entries
  * (>= n + E*(block_size-1)), expert_ids has expert_ids_len entries; entries past the valid
  * prefix are set to n / -1.  Optional outputs (may be NULL): counts[E] tokens per expert,
- * inv_pos[n] position of every flat assignment in sorted_ids.
+ * inv_pos[n] position of every flat assignment in sorted_ids (-1 for an id outside [0, E), which
+ * is reported through fr_check_status and left out of the sort).
  * workspace (may be NULL): fr_align_workspace_bytes(E) bytes of scratch, 16-byte aligned, that
  * lets batches of >= 8192 assignments run as one cooperative launch over all SMs instead of one
- * 8-CTA cluster.  Its first 8 bytes are a grid-barrier word pair: ZERO THE BUFFER ONCE before
- * its first use (and again after fr_check_status has reported an expired wait); completed calls
- * leave it ready for the next one.  One workspace serves one stream at a time. */
+ * 8-CTA cluster.  Its first 16 bytes are control words (grid-barrier count and generation, a
+ * completion counter, and the barrier's poll budget: 0 = the default, about a second): ZERO THE
+ * BUFFER ONCE before its first use (and again after fr_check_status has reported an expired
+ * wait); completed calls leave it ready for the next one.  One workspace serves one stream at
+ * a time. */
 size_t fr_align_workspace_bytes(int E);
 int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids,
              int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_tokens_post_pad,
@@ -91,13 +94,14 @@ int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t*
  * carve, from a plugin whose host forbids device allocation after start-up, or on a hot path
  * that must never reach the allocator).  It has no counterpart in the reference.  It runs the
  * same whole-GPU cooperative kernel as fr_align, with the histogram and barrier words kept in a
- * 257 KB array that the library itself owns on every GPU that loads it, until the process
- * exits.  It calls no cudaMalloc / cudaFree and no allocating library routine.
+ * 262,400-byte (256.25 KB) array that the library itself owns on every GPU that loads it, until
+ * the process exits.  It calls no cudaMalloc / cudaFree and no allocating library routine.
  * Limits: E <= FR_ALIGN_NOALLOC_MAX_EXPERTS and 1 <= n <= 8192 * (number of SMs); anything
  * larger returns FR_ERR_UNSUPPORTED (use fr_align with a workspace).  Outputs are identical
  * to fr_align's.
  * The first call on each device looks up the array's device address (make that call with the
- * device current, before any stream capture starts).  All calls on a device share the one
+ * device current, before any stream capture starts; a first call made while the stream is being
+ * captured returns FR_ERR_UNSUPPORTED).  All calls on a device share the one
  * array: calls whose kernels could overlap on the GPU (different streams) race on it and must
  * be serialised by the caller.  The barrier words are cleared at the start of every call. */
 #define FR_ALIGN_NOALLOC_MAX_EXPERTS 256
@@ -228,28 +232,36 @@ int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row
                    const void* w2, int dtype, int64_t R, int H, int I, int E_local, void* y, void* workspace,
                    size_t workspace_bytes, void* stream);
 
-/* Expert parallelism over peer memory (NVLink loads, no send/receive buffers; no counterpart in
- * the reference).  peer_x / peer_y are DEVICE arrays of `world` base pointers, one per rank, to
- * buffers of identical shape [peer_rows, H] that every GPU of the node can read (symmetric
- * memory); entry `rank` of the table may be the local buffer.
- * fr_moe_experts_peer: the R rows this rank's experts must process are described by
- * (src_rank[r], src_row[r]) = where the token lives, row_expert[r] in [0, E_local) and
- * row_weight[r] (may be NULL).  The gather that builds the expert-sorted A operand reads them
- * from their owners; both grouped GEMMs run; results stay in expert-sorted order in
- * y_sorted[y_rows, H] (y_rows >= fr_moe_experts_rows_cap(R, E_local)); inv_pos_out[r] is the
- * row of y_sorted holding the result of received row r.  Workspace as fr_moe_experts.
- * fr_combine_peer: out[t,:] = sum_j peer_y[rank_of[t*topk+j]][pos_of[t*topk+j], :] in fp32, slot
- * order.  The caller orders the ranks (a small collective before and after): peers' x must be
- * complete before the gather, peers' y_sorted before the combine. */
+/* Expert parallelism over peer memory with no host in the loop (no counterpart in the reference, which
+ * is single-GPU; the sharded layer is fast_route/fast_route/layers/stable_route.py:10-102).
+ * Rank r of `world` owns experts [r*E/world, (r+1)*E/world) and brings its own tokens.  Every rank keeps a
+ * region of identical layout that all GPUs of the node can read (symmetric memory); peer_base is a DEVICE
+ * array of `world` region base pointers (entry `rank` may be the local one).  Inside a region, at byte offsets:
+ *   x_off       x[peer_rows, H]   the rank's tokens (row pitch ld_x elements)
+ *   sorted_off  int32[n_per_rank] its flat assignment ids ordered by expert (fr_align with block_size 1)
+ *   tw_off      float[n_per_rank] its routing weights by flat assignment id
+ *   y_off       y[y_rows, H]      the results of the rank's OWN experts in expert-sorted order
+ * all_counts[world][E] (device, e.g. from one all-gather of every rank's fr_align counts) is the only
+ * metadata that travels.  From it each rank derives on the device where every (local expert, source rank)
+ * segment sits in its operand and, as token owner, in which row of the expert owner's y each of its
+ * assignments ends up, so no sizes reach the host and no position list is sent back.
+ * fr_ep_experts ("pack"): plan -> gather of the token rows from their owners (16-byte NVLink loads) into the
+ *   expert-sorted operand -> GEMM1+SiLU -> GEMM2 x routing weight -> y_sorted (= this rank's y, y_rows rows,
+ *   a multiple of 128; fr_moe_experts_rows_cap(world * n_per_rank, E / world) always suffices; more rows than
+ *   that capacity are dropped and reported as status 4).  comb_base[E] is written for fr_ep_combine.
+ * fr_ep_combine ("unpack"): out[t,:] = sum_j y of the owner of topk_ids[t,j], row comb_base[e] + inv_pos[t*k+j],
+ *   fp32 in slot order; inv_pos is the one fr_align(block_size 1) returned on this rank.
+ * The caller orders the ranks with two small collectives: every region's x / sorted / tw complete before any
+ * fr_ep_experts (the all-gather of the counts does that), every y complete before any fr_ep_combine. */
 int64_t fr_moe_experts_rows_cap(int64_t R, int E_local);
-int fr_moe_experts_peer(const void* const* peer_x, int64_t ld_x, int world, int64_t peer_rows,
-                        const int32_t* src_rank, const int32_t* src_row, const int32_t* row_expert,
-                        const float* row_weight, const void* w1, const void* w2, int dtype, int64_t R, int H,
-                        int I, int E_local, void* y_sorted, int64_t y_rows, int32_t* inv_pos_out,
-                        void* workspace, size_t workspace_bytes, void* stream);
-int fr_combine_peer(const void* const* peer_y, int64_t ld_y, int world, int64_t peer_rows, int dtype,
-                    const int32_t* rank_of, const int32_t* pos_of, int64_t M, int topk, int H, void* out,
-                    int64_t ld_out, void* stream);
+size_t fr_ep_workspace_bytes(int64_t cap_rows, int H, int I, int E);
+int fr_ep_experts(const void* const* peer_base, int world, int rank, int64_t x_off, int64_t ld_x, int64_t peer_rows,
+                  int64_t sorted_off, int64_t tw_off, int64_t n_per_rank, int topk, const int32_t* all_counts,
+                  const void* w1, const void* w2, int dtype, int H, int I, int E, void* y_sorted, int64_t y_rows,
+                  int32_t* comb_base, void* workspace, size_t workspace_bytes, void* stream);
+int fr_ep_combine(const void* const* peer_base, int world, int64_t y_off, int64_t ld_y, int64_t y_rows, int dtype,
+                  const int32_t* topk_ids, const int32_t* inv_pos, const int32_t* comb_base, int64_t M, int topk, int H,
+                  int E, void* out, int64_t ld_out, void* stream);
 
 /* Gather rows by index: dst[i,:] = src[idx[i],:] (idx < 0 writes zeros); 16-byte vectors. */
 int fr_gather_rows(const void* src, int64_t ld_src, const int32_t* idx, int64_t rows, int row_bytes, void* dst,

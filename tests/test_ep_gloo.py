@@ -1,7 +1,9 @@
 """Expert-parallel bookkeeping on CPU ranks (gloo, world size 2 and 4): the split sizes,
 the count exchange, the order of received rows and the return path of
 fast_route_b200.parallel.ep, with the CPU oracle standing in for the device kernels.
-The result must equal the single-process oracle layer on the concatenated batch."""
+The result must equal the single-process oracle layer on the concatenated batch.
+Also here: the plan of the peer-memory path (every rank derives all positions from the gathered
+histograms alone) and what the surviving rank sees when a peer leaves or never joins."""
 
 import os
 import socket
@@ -121,3 +123,143 @@ def test_ep_helpers():
     assert ep.send_splits(torch.tensor([1, 2, 3, 4]), 2) == [3, 7]
     with pytest.raises(RuntimeError):
         ep.validate_counts(torch.tensor([1, 2]), 4, torch.tensor([[0]]))
+
+
+# ------------------------------------------------------------------------------------
+# peer-memory path: positions derived from the all-gathered histograms (ep.plan_tables)
+# ------------------------------------------------------------------------------------
+def _plan_rank_main(rank, world, port, M, H, I, E, k, skew, out_q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    try:
+        import oracle
+        from fast_route_b200 import synth
+        from fast_route_b200.parallel import ep
+
+        group = ep.ExpertParallelGroup(dist.group.WORLD, E)
+        El = group.experts_per_rank
+        bias = synth.zipf_gate_bias(E, 1.2, 3.0) if skew else None
+        x_all, gate, w1, w2 = synth.moe_inputs(M * world, H, I, E, seed=5, dtype=torch.float32, weight_std=0.1,
+                                               gate_bias=bias)
+        x = x_all[rank * M:(rank + 1) * M].contiguous()
+        lo, hi = group.local_expert_range()
+        tw, ti, _ = oracle.route_from_hidden(x, gate, k)
+        n = M * k
+        sorted_ids, _, _, counts = oracle.moe_align_block_size(ti, 1, E)
+        inv = np.empty(n, dtype=np.int64)
+        inv[sorted_ids[:n]] = np.arange(n)
+        # the one metadata collective: everybody's histogram
+        all_counts = torch.empty(world, E, dtype=torch.int32)
+        dist.all_gather_into_tensor(all_counts.view(-1), torch.from_numpy(counts.astype(np.int32)))
+        plan = ep.plan_tables(all_counts.numpy(), rank)
+        # "peer memory": what the kernels would read from the other ranks' regions
+        xs = [torch.empty_like(x) for _ in range(world)]
+        sorts = [torch.empty(n, dtype=torch.int64) for _ in range(world)]
+        tws = [torch.empty(n) for _ in range(world)]
+        dist.all_gather(xs, x)
+        dist.all_gather(sorts, torch.from_numpy(sorted_ids[:n].astype(np.int64)))
+        dist.all_gather(tws, torch.from_numpy(np.ascontiguousarray(tw)).reshape(-1).float())
+        num_post = plan["num_post"]
+        y = torch.zeros(max(num_post, 1), x.shape[1])
+        filled = np.zeros(max(num_post, 1), dtype=bool)
+        for i in range(El * world):
+            j, s_ = divmod(i, world)
+            for off in range(int(plan["seg_count"][i])):
+                row = int(plan["seg_start"][i]) + off
+                sid = int(sorts[s_][int(plan["seg_src_off"][i]) + off])
+                assert int(plan["expert_ids"][row // 128]) == j and not filled[row]
+                filled[row] = True
+                h = oracle.silu_and_mul(xs[s_][sid // k][None] @ w1[lo + j].t())
+                y[row] = (h @ w2[lo + j].t())[0] * tws[s_][sid]
+        ys = [torch.empty(0)] * world
+        sizes = [torch.zeros(1, dtype=torch.int64) for _ in range(world)]
+        dist.all_gather(sizes, torch.tensor([y.shape[0]]))
+        ys = [torch.empty(int(sz), x.shape[1]) for sz in sizes]
+        for src in range(world):                      # variable sizes: one broadcast per owner
+            buf = y if src == rank else ys[src]
+            dist.broadcast(buf, src=src)
+            ys[src] = buf
+        out = torch.zeros(M, x.shape[1])
+        for t in range(M):
+            for jj in range(k):
+                e = int(ti[t, jj])
+                out[t] += ys[e // El][int(plan["comb_base"][e]) + int(inv[t * k + jj])]
+        ref, _, _ = oracle.moe_layer(x_all, gate, w1, w2, k)
+        err = (out - ref[rank * M:(rank + 1) * M]).abs().max().item()
+        out_q.put((rank, err, int(filled.sum()), int(all_counts[:, lo:hi].sum())))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,E,k,skew", [(2, 8, 2, False), (4, 8, 2, False), (2, 16, 4, True), (4, 4, 1, False)])
+def test_ep_plan_from_gathered_histograms_reproduces_single_process_layer(world, E, k, skew):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_plan_rank_main, args=(r, world, port, 24, 32, 48, E, k, skew, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, rows_filled, rows_expected in sorted(results):
+        assert err < 1e-5, (rank, err)
+        assert rows_filled == rows_expected
+
+
+def test_plan_tables_small_example():
+    from fast_route_b200.parallel import ep
+    c = np.array([[3, 0, 5, 2], [1, 4, 0, 130]])
+    p0, p1 = ep.plan_tables(c, 0), ep.plan_tables(c, 1)
+    assert p0["seg_start"].tolist() == [0, 3, 128, 128, 256] and p0["seg_count"].tolist() == [3, 1, 0, 4]
+    assert p0["seg_src_off"].tolist() == [0, 0, 3, 1] and p0["comb_base"].tolist() == [0, 125, -3, 120]
+    assert p1["num_post"] == 384 and p1["expert_ids"].tolist() == [0, 1, 1]
+    assert p1["seg_start"].tolist() == [0, 5, 128, 130, 384] and p1["comb_base"].tolist() == [3, 127, 0, 125]
+
+
+# ------------------------------------------------------------------------------------
+# a peer that leaves between steps, a peer that never joins: the survivor gets an exception
+# ------------------------------------------------------------------------------------
+def _leaver_main(rank, world, port, mode, out_q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    import time
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    counts = torch.full((4,), rank + 1, dtype=torch.int32)
+    allc = torch.empty(world, 4, dtype=torch.int32)
+    dist.all_gather_into_tensor(allc.view(-1), counts)          # step 1: everybody is there
+    assert allc[:, 0].tolist() == list(range(1, world + 1))
+    if rank == world - 1:
+        if mode == "exit":
+            dist.destroy_process_group()                       # leaves between steps, nothing in flight
+            out_q.put((rank, "left"))
+            return
+        time.sleep(8)                                          # never joins step 2 within the group's timeout
+        out_q.put((rank, "late"))
+        return
+    try:
+        dist.all_gather_into_tensor(allc.view(-1), counts)      # step 2
+        out_q.put((rank, "completed"))
+    except Exception as err:                                   # noqa: BLE001 - any exception is the point
+        out_q.put((rank, "raised:" + type(err).__name__))
+
+
+@pytest.mark.parametrize("mode", ["exit", "timeout"])
+def test_ep_peer_leaves_or_never_joins(mode):
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaver_main, args=(r, world, port, mode, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=60) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+    assert results[0].startswith("raised:"), results
+    assert results[1] in ("left", "late")
