@@ -6,8 +6,11 @@
 
 One JSON line is printed by rank 0.  A step is one pass of the layer over one batch of
 synthetic tokens (x ~ N(0,1), weights ~ N(0, 0.02^2), bf16).  With N > 1 the experts are
-sharded over the ranks (expert parallel, NCCL all-to-all dispatch and combine) and every
-rank brings its own batch of M tokens (weak scaling in tokens).
+sharded over the ranks (expert parallel; token rows move by peer-memory loads inside the gather
+and combine kernels, or by NCCL all-to-all with --ep-mode nccl) and every rank brings its own
+batch of M tokens (weak scaling in tokens).  Every line also carries `parity` (the timed layer's
+output checked outside the timed region) and `config5` (Mixtral-8x22B shape, 32768 tokens per
+box split over the ranks).
 """
 
 from __future__ import annotations
@@ -28,6 +31,8 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# DRAM bytes of one GEMM1 launch at 16384 tokens, Mixtral-8x7B shape (one-pass ncu capture: 3.20 GB read + 0.95 GB written)
+GEMM1_DRAM_BYTES_M16384 = 4.15e9
 WORKLOADS = {
     # name: (H, I, E, topk)
     "mixtral-8x7b": (4096, 14336, 8, 2),
@@ -419,6 +424,53 @@ def gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps):
             "ms_per_launch": med, "algorithmic_flops_per_launch": flops, "traffic": None}
 
 
+def stage_times_single_gpu(fr, wg, w1, w2, M, H, I, E, k, reps=5):
+    """CUDA-event time of every stage of the layer under the reference's stage names
+    (fast_route/fast_route/layers/profile_fused_route.py:61-121: route, moe_align, moe_1, silu_and_mul, moe_2),
+    each stage issued alone through the operator surface; silu_and_mul is part of moe_1 here and `gather` /
+    `combine` are the two memory-bound passes around the GEMMs."""
+    from fast_route_b200.ops import fused_moe as fm
+    dev = w1.device
+    x = torch.randn(M, H, device=dev, dtype=w1.dtype)
+    n = M * k
+    rows = (n + min(n, E) * 127 + 127) // 128 * 128
+    tw, ti = fr.fused_route(x, wg.t(), k)
+    s, e, npost, cnt, inv = fm.moe_align_block_size(ti, 128, E, return_extra=True)
+    a = fm.permute_rows(x, s, npost, k, max_rows=rows)
+    act = fm.gemm1_silu(a, w1, e, npost, s, n)
+    y = fm.gemm2(act, w2, e, npost, s, tw, n)
+    out = {}
+    out["route"] = cuda_time_ms(lambda: fr.fused_route(x, wg.t(), k), reps, 2)[0]
+    out["moe_align"] = cuda_time_ms(lambda: fm.moe_align_block_size(ti, 128, E, return_extra=True), reps, 2)[0]
+    out["gather"] = cuda_time_ms(lambda: fm.permute_rows(x, s, npost, k, max_rows=rows), reps, 2)[0]
+    out["moe_1+silu_and_mul"] = cuda_time_ms(lambda: fm.gemm1_silu(a, w1, e, npost, s, n), reps, 2)[0]
+    out["moe_2"] = cuda_time_ms(lambda: fm.gemm2(act, w2, e, npost, s, tw, n), reps, 2)[0]
+    out["combine"] = cuda_time_ms(lambda: fm.combine(y, inv, M, k), reps, 2)[0]
+    return {k_: round(v, 4) for k_, v in out.items()}
+
+
+def router_from_hidden_states(fr, dev, dtype):
+    """The reference's router op bench (benchmarks/fused_route/op_bench.py:62-130): fused_route from hidden
+    states [m, 4096] to the top-k weights / ids, swept over the batch and the expert count."""
+    rows = []
+    K = 4096
+    g = torch.Generator(device=dev).manual_seed(11)
+    for E, k in ((8, 2), (64, 6), (128, 8)):
+        gate = (torch.randn(E, K, device=dev, generator=g) * 0.02).to(dtype)
+        for m in (1, 64, 1024, 4096, 16384):
+            x = torch.randn(m, K, device=dev, dtype=dtype, generator=g)
+            gr = torch.cuda.CUDAGraph()
+            fr.fused_route(x, gate.t(), k)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(gr):
+                fr.fused_route(x, gate.t(), k)
+            us = cuda_time_ms(gr.replay, 30, 5)[0] * 1e3
+            del gr
+            nbytes = m * K * 2 + E * K * 2 + m * k * 8
+            rows.append({"tokens": m, "E": E, "topk": k, "us": round(us, 2), "hbm_gbs": nbytes / us / 1e3})
+    return rows
+
+
 def bind_to_gpu_numa_node(index):
     """Pins this process to the CPUs of the NUMA node the GPU hangs off, so that the pinned host buffers it allocates
     next (first touch) and the copy threads sit next to the GPU's PCIe root.  Returns the node or None."""
@@ -439,6 +491,160 @@ def bind_to_gpu_numa_node(index):
         return node
     except Exception:
         return None
+
+
+def fp32_rows(x, tw, ti, w1, w2, rows):
+    """Direct fp32 evaluation of the layer for a few token rows on the device (full experts in w1 / w2)."""
+    I = w1.shape[1] // 2
+    ref = torch.zeros(len(rows), x.shape[1], device=x.device)
+    cache = {}
+    for i, r in enumerate(rows):
+        for j in range(ti.shape[1]):
+            e = int(ti[r, j])
+            if e not in cache:
+                if len(cache) >= 3:
+                    cache.clear()
+                cache[e] = (w1[e].float(), w2[e].float())
+            a1, a2 = cache[e]
+            h1 = a1 @ x[r].float()
+            ref[i] += tw[r, j] * (a2 @ (torch.nn.functional.silu(h1[:I]) * h1[I:]))
+    return ref
+
+
+def parity_report(fr, layer, x, wg, w1_full, w2_full, k, world, dist):
+    """Outside every timed region: the timed layer's output against (a) a direct fp32 evaluation of sampled token
+    rows and (b), with N > 1, the single-GPU layer on this rank's tokens with all experts loaded; routing ids
+    against a stable descending sort of the device's own logits.  Maxima / minima are taken over the ranks."""
+    dev = x.device
+    M = x.shape[0]
+    out = layer(x)
+    tw, ti, logits = fr.fused_route(x, wg.t(), k, return_logits=True)
+    order = torch.sort(logits, dim=1, descending=True, stable=True)
+    ids_ok = bool(torch.equal(order[1][:, :k].to(torch.int32), ti))
+    wt = torch.softmax(order[0][:, :k], dim=-1)
+    rows = sorted(set(list(range(0, M, max(1, M // 8)))[:8] + [M - 1]))
+    ref = fp32_rows(x, tw, ti, w1_full, w2_full, rows)
+    diff = (out[rows].float() - ref).abs()
+    ref_rms = float(ref.pow(2).mean().sqrt())
+    rep = {"rows": len(rows), "max_abs": float(diff.max()), "mean_rel": float(diff.mean() / ref.abs().mean()),
+           "ref_abs_max": float(ref.abs().max()), "ref_rms": ref_rms, "max_abs_over_ref_rms": float(diff.max()) / ref_rms,
+           "frac_within_flat_2e-2": float((diff <= 2e-2).float().mean()),
+           "within_2e-2_plus_one_bf16_spacing": bool((diff <= 2e-2 + ref.abs() * 2.0 ** -7).all()),
+           "ids_bit_exact": ids_ok, "weights_max_abs_vs_softmax": float((tw - wt).abs().max()),
+           "note": "reference = direct fp32 evaluation of the sampled token rows on the device; the flat 2e-2 is stated "
+                   "for outputs of order 0.2 (the reference's CPU case); here one bf16 spacing of an output is "
+                   "|value| / 128"}
+    if world > 1:
+        single = fr.fused_moe(x, wg.t(), w1_full, w2_full, k)
+        d = (out.float() - single.float()).abs().max()
+        stats = torch.tensor([rep["max_abs"], rep["mean_rel"], float(d), 0.0 if torch.equal(out, single) else 1.0,
+                              0.0 if ids_ok else 1.0, 1.0 - rep["frac_within_flat_2e-2"],
+                              0.0 if rep["within_2e-2_plus_one_bf16_spacing"] else 1.0], device=dev)
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        v = stats.tolist()
+        rep.update({"max_abs": v[0], "mean_rel": v[1], "ep_vs_single_gpu_max_abs": v[2],
+                    "ep_vs_single_gpu_bit_equal": v[3] == 0.0, "ids_bit_exact": v[4] == 0.0,
+                    "frac_within_flat_2e-2": 1.0 - v[5], "within_2e-2_plus_one_bf16_spacing": v[6] == 0.0,
+                    "over": "max over ranks"})
+    return rep
+
+
+def timed_layer_steps(layer, xs, steps, warmup, barrier, world, dist, dev):
+    """W warm-up and K timed steps bracketed by barrier + synchronize; device time, max over ranks (ms per step)."""
+    for i in range(warmup):
+        layer(xs[i % len(xs)])
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for i in range(steps):
+        layer(xs[i % len(xs)])
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def make_layer(fr, ep, group, world, wg, w1_full, w2_full, k, ep_mode):
+    """(layer(x) -> out, local expert weights, kernel launches per step) for this rank."""
+    if world == 1:
+        return (lambda xb: fr.fused_moe(xb, wg.t(), w1_full, w2_full, k)), w1_full, w2_full, 6
+    lo, hi = group.local_expert_range()
+    w1, w2 = w1_full[lo:hi], w2_full[lo:hi]          # contiguous slices of the full tensors
+    if ep_mode == "p2p":
+        return (lambda xb: ep.fused_moe_ep_p2p(xb, wg.t(), w1, w2, k, group)), w1, w2, 7
+    return (lambda xb: ep.fused_moe_ep(xb, wg.t(), w1, w2, k, group)), w1, w2, 12
+
+
+def config5_point(fr, ep, synth, group, world, rank, dev, dtype, peaks, steps, warmup, barrier, dist, ep_mode, single_ms):
+    """Expert-parallel Mixtral-8x22B-shaped layer: 32768 tokens per box split evenly over the ranks, experts sharded
+    E/W per rank, device-timed max over ranks, with the stages timed by CUDA events in a separate pass."""
+    H, I, E, k = WORKLOADS["mixtral-8x22b"]
+    box_tokens = 32768
+    M = box_tokens // world
+    wg, w1_full, w2_full = make_weights(H, I, E, dev, seed=5)
+    layer, w1, w2, launches = make_layer(fr, ep, group, world, wg, w1_full, w2_full, k, ep_mode)
+    g = torch.Generator(device=dev).manual_seed(500 + rank)
+    xs = [torch.randn(M, H, device=dev, dtype=dtype, generator=g) for _ in range(2)]
+    ms = timed_layer_steps(layer, xs, steps, warmup, barrier, world, dist, dev)
+    flops = synth.layer_flops(box_tokens, H, I, E, k)
+    rep = {"workload": f"mixtral-8x22b MoE layer H={H} I={I} E={E} top-{k}, {box_tokens} tokens per box = {M} per rank, "
+                       f"experts sharded {E // world} per rank", "n_gpus": world, "steps": steps, "warmup": warmup,
+           "ms_per_step": ms, "tokens_per_s": box_tokens / ms * 1e3, "tflops": flops / ms / 1e9,
+           "frac_of_n_x_sustained_peak": flops / ms / 1e9 / (peaks["bf16_tflops_sustained"] * world),
+           "frac_of_n_x_burst_peak": flops / ms / 1e9 / (peaks["bf16_tflops"] * world),
+           "scaling": "strong (total work fixed)", "timing": "CUDA events, max over ranks"}
+    # stage times: a separate pass with events between the stages (max over ranks of each stage's median)
+    if world > 1 and ep_mode == "p2p":
+        acc = {}
+        for i in range(4):
+            timers = []
+            ep.fused_moe_ep_p2p(xs[i % 2], wg.t(), w1, w2, k, group, timers=timers)
+            torch.cuda.synchronize()
+            if i:                      # first pass warms the event path
+                for name, a, b in timers:
+                    acc.setdefault(name, []).append(a.elapsed_time(b))
+        names = list(acc)
+        t = torch.tensor([statistics.median(acc[nm]) for nm in names], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        rep["stage_ms_max_over_ranks"] = {nm: round(v, 4) for nm, v in zip(names, t.tolist())}
+    elif world == 1:
+        rep["stage_ms"] = stage_times_single_gpu(fr, wg, w1_full, w2_full, M, H, I, E, k)
+    rep["parity"] = parity_report(fr, layer, xs[0], wg, w1_full, w2_full, k, world, dist)
+    del xs, w1_full, w2_full
+    return rep
+
+
+def host_copy_ceiling(M, H, dtype, dev, steps, barrier, world, dist):
+    """What the host side alone sustains: every rank copies one batch in and one batch out per step, concurrently,
+    with no compute.  ms per step, max over ranks."""
+    hx = torch.randn(M, H, dtype=dtype).pin_memory()
+    ho = torch.empty(M, H, dtype=dtype).pin_memory()
+    dx = torch.empty(M, H, dtype=dtype, device=dev)
+    dy = torch.empty(M, H, dtype=dtype, device=dev)
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+
+    def step():
+        with torch.cuda.stream(s_in):
+            dx.copy_(hx, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            ho.copy_(dy, non_blocking=True)
+    step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    torch.cuda.synchronize()
+    ms = (time.perf_counter() - t0) * 1e3 / steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms
 
 
 def run_ours(args, rank, world, local_rank):
@@ -462,37 +668,32 @@ def run_ours(args, rank, world, local_rank):
         return
 
     numa_node = None
+    ep = group = None
+    # every rank holds the full expert set (same seed): its own shard is a slice of it, and the parity check
+    # outside the timed region runs the single-GPU layer on the rank's tokens against it
+    wg, w1_full, w2_full = make_weights(H, I, E, dev, seed=0)
     if world > 1:
         # one process per GPU: keep each process (and the pinned buffers it allocates) on its GPU's NUMA node
         numa_node = bind_to_gpu_numa_node(local_rank)
         from fast_route_b200.parallel import ep
         assert E % world == 0, "experts must divide over the ranks"
         group = ep.ExpertParallelGroup(dist.group.WORLD, E)
-        lo, hi = group.local_expert_range()
-        wg, w1, w2 = make_weights(H, I, E, dev, seed=0, experts=list(range(lo, hi)))
-        # the gate is replicated: same seed stream on every rank would differ after the experts, so broadcast it
-        dist.broadcast(wg, src=0)
-
         if args.ep_mode == "p2p":
-            def layer(xb):
-                return ep.fused_moe_ep_p2p(xb, wg.t(), w1, w2, k, group)
-            launches_per_step = 9
-            try:        # symmetric memory needs peer access between all GPUs of the node
-                layer(torch.zeros(M, H, device=dev, dtype=dtype))
-            except Exception as err:        # every rank fails the same way at the collective set-up
-                if rank == 0:
-                    print(f"peer-memory path unavailable ({err}); using NCCL all-to-all", file=sys.stderr)
+            # symmetric memory needs peer access between all GPUs of the node; whether it works is decided by
+            # ALL ranks together, so that nobody is left alone in a collective of the other mode
+            ok = torch.ones(1, device=dev)
+            try:
+                lo, hi = group.local_expert_range()
+                ep.fused_moe_ep_p2p(torch.zeros(M, H, device=dev, dtype=dtype), wg.t(), w1_full[lo:hi], w2_full[lo:hi],
+                                    k, group)
+                torch.cuda.synchronize()
+            except Exception as err:
+                ok.zero_()
+                print(f"rank {rank}: peer-memory path unavailable ({err})", file=sys.stderr)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if ok.item() == 0:
                 args.ep_mode = "nccl"
-        if args.ep_mode == "nccl":
-            def layer(xb):
-                return ep.fused_moe_ep(xb, wg.t(), w1, w2, k, group, chunks=args.ep_chunks)
-            launches_per_step = 12 * (args.ep_chunks or 1)
-    else:
-        wg, w1, w2 = make_weights(H, I, E, dev, seed=0)
-
-        def layer(xb):
-            return fr.fused_moe(xb, wg.t(), w1, w2, k)
-        launches_per_step = 6
+    layer, w1, w2, launches_per_step = make_layer(fr, ep, group, world, wg, w1_full, w2_full, k, args.ep_mode)
 
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     xs = [torch.randn(M, H, device=dev, dtype=dtype, generator=g) for _ in range(3)]
@@ -542,6 +743,10 @@ def run_ours(args, rank, world, local_rank):
             print(json.dumps({"profile_run": True, "ms_per_step": ms_per_step, "tokens_per_s": value}), flush=True)
         return
 
+    # ---- parity of the very configuration that was timed (outside the timed region) ---
+    parity = parity_report(fr, layer, xs[0], wg, w1_full, w2_full, k, world, dist)
+    _lib.raise_on_device_error()
+
     # ---- end to end through the public API with host buffers ------------------------
     # Every step copies its own input batch from pinned host memory and its result back.  The calls are pipelined
     # the way a serving loop issues them: step i+1's input travels while step i computes, step i's result travels
@@ -555,19 +760,9 @@ def run_ours(args, rank, world, local_rank):
         else:
             ep.fused_moe_ep_host(hx[i % 2], wg.t(), w1, w2, k, group, out_host=hout[i % 2],
                                  p2p=(args.ep_mode == "p2p"), pipelined=True)
-    try:
-        for i in range(max(1, min(args.warmup, 3))):
-            e2e_step(i)
-        fr.fused_moe_host_wait(dev)
-    except Exception as err:      # every rank runs the same host code, so all of them land here together
-        if rank == 0:
-            print(f"pipelined host path failed ({err}); copies on the compute stream instead", file=sys.stderr)
-        dx = torch.empty(M, H, dtype=dtype, device=dev)
-
-        def e2e_step(i):
-            dx.copy_(hx[i % 2], non_blocking=True)
-            hout[i % 2].copy_(layer(dx), non_blocking=True)
-        e2e_step(0)
+    for i in range(max(1, min(args.warmup, 3))):
+        e2e_step(i)
+    fr.fused_moe_host_wait(dev)
     barrier()
     e0.record()
     for i in range(args.steps):
@@ -582,9 +777,34 @@ def run_ours(args, rank, world, local_rank):
         ems = float(t.item())
     e2e = {"value": total_tokens / (ems / args.steps) * 1e3, "unit": "tokens/s",
            "h2d_bytes_per_step": M * H * 2 * world, "d2h_bytes_per_step": M * H * 2 * world,
-           "ms_per_step": ems / args.steps}
+           "ms_per_step": ems / args.steps, "mode": "pipelined calls (copies of neighbouring steps overlap the compute)"}
+    if world == 1:
+        # one isolated call at a time: copy in, layer, copy out, synchronise (copies chunked inside the call)
+        def isolated():
+            fr.fused_moe_host(hx[0], wg.t(), w1, w2, k, out_host=hout[0])
+            torch.cuda.synchronize()
+        isolated()
+        ts = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            isolated()
+            ts.append((time.perf_counter() - t0) * 1e3)
+        e2e["isolated_call_ms"] = statistics.median(ts)
+        e2e["isolated_call_tokens_per_s"] = M / statistics.median(ts) * 1e3
+    copy_ms = host_copy_ceiling(M, H, dtype, dev, max(3, args.steps // 2), barrier, world, dist)
+    e2e["host_copies_alone_ms_per_step"] = copy_ms
+    e2e["host_copy_ceiling_tokens_per_s"] = total_tokens / copy_ms * 1e3
+    e2e["frac_of_min_of_device_and_copy_ceiling"] = e2e["value"] / min(value, total_tokens / copy_ms * 1e3)
     if numa_node is not None:
         e2e["host_numa_node_rank0"] = numa_node
+    del hx, hout
+
+    # ---- the expert-parallel configuration of the scaling study (every N, N = 1 included) ----
+    config5 = None
+    if args.workload == "mixtral-8x7b" and not args.no_config5 and 8 % world == 0:
+        config5 = config5_point(fr, ep, synth, group, world, rank, dev, dtype, peaks, max(5, args.steps // 2),
+                                3, barrier, dist, args.ep_mode, None)
+        _lib.raise_on_device_error()
 
     if rank != 0:
         return
@@ -603,19 +823,23 @@ def run_ours(args, rank, world, local_rank):
         "frac_tensor_peak": flops / ms_per_step / 1e9 / (peaks["bf16_tflops_sustained"] * world),
         "frac_tensor_peak_note": f"of {peaks['source']} sustained cuBLAS bf16 ({peaks['bf16_tflops_sustained']} TF/GPU)",
         "clocks": clocks, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "expert_load": expert_load,
+        "parity": parity,
     }
+    if config5 is not None:
+        line["config5"] = config5
     if world == 1:
         line["roofline"] = gemm1_roofline(fr, synth, wg, w1, w2, M, H, I, E, k, peaks, reps=max(5, args.steps))
         if args.workload == "mixtral-8x7b" and M == 16384:
-            # dram__bytes_read.sum + dram__bytes_write.sum of this launch from a one-pass ncu capture
-            # (profiles/grouped_gemm_dram_traffic_mixtral8x7b.md): 3.20 GB read + 0.95 GB written
-            line["roofline"]["traffic"] = 4.15e9
-            line["roofline"]["traffic_note"] = ("DRAM bytes per GEMM1 launch (ncu, one pass); algorithmic bytes are "
-                                                "2.16 GB read (weights + A once) + 0.97 GB written")
+            line["roofline"]["traffic"] = GEMM1_DRAM_BYTES_M16384
+            line["roofline"]["traffic_note"] = ("dram__bytes_read.sum + dram__bytes_write.sum of one GEMM1 launch at "
+                                                "this size from a one-pass ncu capture (not measured in this run); "
+                                                "algorithmic bytes are 2.16 GB read (weights + A once) + 0.97 GB written")
         if not args.no_sweep and args.workload == "mixtral-8x7b":
-            Ms = [m for m in (1, 4, 16, 64, 256, 1024, 4096, 16384)]
+            Ms = [1, 4, 16, 64, 256, 1024, 2048, 4096, 8192, 16384]
             line["sweep"] = sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms)
+            line["stage_ms"] = stage_times_single_gpu(fr, wg, w1, w2, M, H, I, E, k)
             line["routing_latency"] = routing_latency(fr, synth, dev)
+            line["router_from_hidden_states"] = router_from_hidden_states(fr, dev, dtype)
             line["transformer_block"] = transformer_block(fr, wg, w1, w2, M, H, k)
             line["fp8_weights_mode"] = fp8_points(fr, synth, wg, w1, w2, H, I, E, k, peaks)
             line["w4a16_splitk_gemm"] = w4a16_splitk(dev, peaks)
@@ -646,10 +870,10 @@ def main():
     ap.add_argument("--ep-mode", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: token rows move by peer-memory loads inside the gather / combine kernels (p2p) "
                          "or through NCCL all-to-all send/receive buffers (nccl)")
-    ap.add_argument("--ep-chunks", type=int, default=None,
-                    help="token chunks pipelined through dispatch/experts/return with N > 1 (default 1)")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-config5", action="store_true",
+                    help="skip the Mixtral-8x22B expert-parallel point (32768 tokens per box) added to every line")
     ap.add_argument("--routing-only", action="store_true",
                     help="only the routing/align latency microbenchmark (16384 tokens, E in 8/64/128)")
     ap.add_argument("--w4a16-only", action="store_true",
@@ -667,6 +891,10 @@ def main():
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # peer memory is only read by plain loads and the collectives are tiny: no NVLink multicast objects, in
+        # NCCL or in symmetric memory, that a rank ending early could leave bound
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:

@@ -52,7 +52,7 @@ SIGNATURES = {
     "fr_moe_experts": (_I, [_P, _P, _P, _P, _P, _I, _L, _I, _I, _I, _P, _P, _Z, _P]),
     "fr_moe_experts_rows_cap": (_L, [_L, _I]),
     "fr_ep_workspace_bytes": (_Z, [_L, _I, _I, _I]),
-    "fr_ep_experts": (_I, [_P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _P, _P, _P, _I, _I, _I, _I, _P, _L, _P, _P, _Z, _P]),
+    "fr_ep_experts": (_I, [_P, _I, _I, _L, _L, _L, _L, _L, _L, _I, _P, _P, _P, _I, _I, _I, _I, _P, _L, _P, _I, _P, _Z, _P]),
     "fr_ep_combine": (_I, [_P, _I, _L, _L, _L, _I, _P, _P, _P, _L, _I, _I, _I, _P, _L, _P]),
     "fr_gather_rows": (_I, [_P, _L, _P, _L, _I, _P, _L, _P]),
     "fr_w4a16_gemm": (_I, [_P, _L, _P, _P, _P, _L, _I, _I, _I, _P, _L, _I, _P]),

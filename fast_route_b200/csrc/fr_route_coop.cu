@@ -7,6 +7,7 @@
 #include <cooperative_groups.h>
 
 #include <atomic>
+#include <cstdlib>
 
 #include "fr_common.cuh"
 
@@ -256,6 +257,7 @@ struct CoopParams {
   int32_t* num_post;
   int32_t* counts;
   int32_t* inv_pos;
+  int32_t* block_rows;    // optional, per block of bs rows: rows that hold tokens, rounded up to 16 (bs if full)
   // scratch
   int32_t* hist;          // [gridDim][E]
   unsigned int* barrier;  // [2]
@@ -263,7 +265,12 @@ struct CoopParams {
   int64_t seg;            // assignments per warp, multiple of 32
 };
 
-__global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
+// The kernel body; load_ids(sids, lo_blk, slice) fills this block's slice of the flat expert ids in shared memory.
+// (Ranking the block's own rows of logits in that phase, to make routing + align one launch, was measured and is
+// not faster than the two kernels: the ranking runs slower inside a one-block-per-SM cooperative kernel than as
+// its own full-occupancy launch, and the cost of a cooperative launch is paid either way.)
+template <typename LoadIds>
+__device__ __forceinline__ void align_coop_body(const CoopParams& p, LoadIds&& load_ids) {
   extern __shared__ int csm[];
   const int nwarps = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -281,14 +288,7 @@ __global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
   const int64_t hi_blk = min(p.n, lo_blk + p.per_block);
   const int slice = hi_blk > lo_blk ? static_cast<int>(hi_blk - lo_blk) : 0;
   for (int i = threadIdx.x; i < nwarps * ES + 2 * E; i += blockDim.x) cnt[i] = 0;  // cnt, total, before
-  for (int i = threadIdx.x; i < slice; i += blockDim.x) {
-    int e = __ldg(p.ids_in + lo_blk + i);
-    if (e < 0 || e >= E) {
-      report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(e));
-      e = -1;
-    }
-    sids[i] = e;
-  }
+  load_ids(sids, lo_blk, slice);
   __syncthreads();
 
   // pass 1: per-warp counts over the warp's contiguous sub-slice (order of the atomics is irrelevant)
@@ -326,13 +326,20 @@ __global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
         int t = 0, bfr = 0;
         const int trips = (B - g + G - 1) / G;      // blocks g, g+G, ... handled by this thread
         int j = (me * 7) % (trips > 0 ? trips : 1);
-#pragma unroll 4
-        for (int it = 0; it < trips; ++it) {
-          const int b = g + j * G;
-          const int v = __ldcg(p.hist + static_cast<int64_t>(b) * E + ee);
-          t += v;
-          if (b < me) bfr += v;
-          if (++j == trips) j = 0;
+        constexpr int BATCH = 8;                    // independent loads issued back to back
+        for (int it = 0; it < trips; it += BATCH) {
+          int v[BATCH], bb[BATCH];
+#pragma unroll
+          for (int u = 0; u < BATCH; ++u) {
+            bb[u] = g + j * G;
+            v[u] = (it + u < trips) ? __ldcg(p.hist + static_cast<int64_t>(bb[u]) * E + ee) : 0;
+            if (++j >= trips) j = 0;
+          }
+#pragma unroll
+          for (int u = 0; u < BATCH; ++u) {
+            t += v[u];
+            if (bb[u] < me) bfr += v[u];
+          }
         }
         atomicAdd(&total[ee], t);
         atomicAdd(&before[ee], bfr);
@@ -389,7 +396,13 @@ __global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
     for (int q = s + t + lane; q < pe; q += 32)
       if (q < p.sorted_len) p.sorted[q] = static_cast<int32_t>(p.n);
     for (int blk = s / p.bs + lane; blk < pe / p.bs; blk += 32)
-      if (blk < p.expert_ids_len) p.expert_ids[blk] = e;
+      if (blk < p.expert_ids_len) {
+        p.expert_ids[blk] = e;
+        if (p.block_rows) {
+          const int tail = t % p.bs;
+          p.block_rows[blk] = (blk == pe / p.bs - 1 && tail) ? min(p.bs, (tail + 15) & ~15) : p.bs;
+        }
+      }
     if (p.counts && lane == 0) p.counts[e] = t;
   }
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -397,6 +410,19 @@ __global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
   for (int64_t q = num_post + gthread; q < p.sorted_len; q += gthreads) p.sorted[q] = static_cast<int32_t>(p.n);
   for (int64_t blk = num_post / p.bs + gthread; blk < p.expert_ids_len; blk += gthreads) p.expert_ids[blk] = -1;
   if (blockIdx.x == 0 && threadIdx.x == 0) *p.num_post = num_post;
+}
+
+__global__ void __launch_bounds__(1024) align_coop_kernel(const CoopParams p) {
+  align_coop_body(p, [&](int32_t* sids, int64_t lo_blk, int slice) {
+    for (int i = threadIdx.x; i < slice; i += blockDim.x) {
+      int e = __ldg(p.ids_in + lo_blk + i);
+      if (e < 0 || e >= p.E) {
+        report(ST_BAD_EXPERT_ID, static_cast<unsigned int>(e));
+        e = -1;
+      }
+      sids[i] = e;
+    }
+  });
 }
 
 constexpr int kCoopMaxPerBlock = 8192;
@@ -410,7 +436,8 @@ size_t coop_workspace_bytes(int E) {
 // cluster kernel.
 int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                         int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st, int64_t min_n) {
+                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st, int64_t min_n,
+                        int32_t* block_rows) {
   if (!workspace || workspace_bytes < coop_workspace_bytes(E) || (reinterpret_cast<uintptr_t>(workspace) & 15))
     return FR_ERR_UNSUPPORTED;
   if (n < min_n || n < 1 || E > 1024) return FR_ERR_UNSUPPORTED;
@@ -440,6 +467,7 @@ int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t
   p.num_post = num_post;
   p.counts = counts;
   p.inv_pos = inv_pos;
+  p.block_rows = block_rows;
   p.barrier = static_cast<unsigned int*>(workspace);
   p.hist = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + 256);
   p.per_block = per_block;
@@ -517,7 +545,7 @@ int align_noalloc_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, in
   // they are read.
   FR_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
   return align_coop_dispatch(topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post,
-                             counts, inv_pos, scratch, kNoAllocScratchBytes, st, /*min_n=*/1);
+                             counts, inv_pos, scratch, kNoAllocScratchBytes, st, /*min_n=*/1, nullptr);
 }
 
 }  // namespace fr

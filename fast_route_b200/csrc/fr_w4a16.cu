@@ -322,12 +322,18 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int n = n0 + t;
     if (n < p.n) {
       for (int row = rank + grp_id * S; row < p.m; row += W4_GROUPS * S) {
-        float acc = 0.0f;
-        for (int r = 0; r < S; ++r) {
-          const float* remote = cluster.map_shared_rank(reinterpret_cast<float*>(sW), r);
-          const float v = remote[row * W4_BN + t];
-          acc = (r == 0) ? v : __fadd_rn(acc, v);
+        // all remote loads in flight together (one trip through the cluster network instead of S), then the
+        // sum in rank order
+        float v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          v[r] = 0.0f;
+          if (r < S) v[r] = cluster.map_shared_rank(reinterpret_cast<float*>(sW), r)[row * W4_BN + t];
         }
+        float acc = v[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r)
+          if (r < S) acc = __fadd_rn(acc, v[r]);
         p.c[static_cast<int64_t>(row) * p.ldc + n] = __float2half_rn(acc);
       }
     }

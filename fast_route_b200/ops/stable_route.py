@@ -37,8 +37,9 @@ def fused_route(hidden_state: torch.Tensor, gate: torch.Tensor, topk: int, topk_
     """``hidden_state[M,K]``, ``gate[K,E]`` -> (weights[:, :topk], ids[:, :topk]).
 
     ``topk_weights`` / ``topk_ids`` are the caller's ``[M,E]`` buffers as in the reference
-    (any float / integer dtype); the first ``topk`` columns receive the result and the
-    returned tensors are views of them.  Passing ``None`` returns fresh compact
+    (any float / integer dtype); the first ``topk`` columns receive the result, the remaining
+    columns what the reference leaves there (the rest of the stable argsort / zeros), and the
+    returned tensors are views of the first ``topk`` columns.  Passing ``None`` returns fresh compact
     contiguous ``[M,topk]`` fp32 / int32 tensors, the layout the expert kernels take.
     The reference only supports ``renormalize=True`` (``ops/stable_route.py:130``);
     ``False`` divides by the softmax denominator over all experts instead.
@@ -51,11 +52,23 @@ def fused_route(hidden_state: torch.Tensor, gate: torch.Tensor, topk: int, topk_
     assert 0 < topk <= N
     assert hidden_state.dtype in (torch.float16, torch.bfloat16) and gate.dtype == hidden_state.dtype
     assert hidden_state.stride(1) == 1, "hidden_state rows must be contiguous"
-    w, ids, logits = _route_compact(hidden_state, gate, topk, renormalize, return_logits)
-    if topk_weights is not None:
-        topk_weights[:, :topk].copy_(w)
-        topk_ids[:, :topk].copy_(ids)
-        w, ids = topk_weights[:, :topk], topk_ids[:, :topk]
+    if topk_weights is None:
+        w, ids, logits = _route_compact(hidden_state, gate, topk, renormalize, return_logits)
+        return (w, ids, logits) if return_logits else (w, ids)
+    # The reference's kernel stores all E columns of the caller's buffers (ops/stable_route.py:110-121): the ids
+    # of the complete stable descending argsort and zeros after the first k weights.  Same here: the gate GEMM
+    # leaves its fp32 logits, the ranking kernel fills the full width from them.
+    assert topk_ids is not None and topk_weights.shape == (M, N) and topk_ids.shape == (M, N)
+    _, _, logits = _route_compact(hidden_state, gate, topk, renormalize, True)
+    direct = (topk_weights.dtype == torch.float32 and topk_ids.dtype == torch.int32 and
+              topk_weights.stride(1) == 1 and topk_ids.stride(1) == 1)
+    if direct:
+        route_from_logits(logits, topk, renormalize, fill_rest=True, topk_weights=topk_weights, topk_ids=topk_ids)
+    else:
+        fw, fi = route_from_logits(logits, topk, renormalize, fill_rest=True)
+        topk_weights.copy_(fw)
+        topk_ids.copy_(fi)
+    w, ids = topk_weights[:, :topk], topk_ids[:, :topk]
     return (w, ids, logits) if return_logits else (w, ids)
 
 

@@ -296,13 +296,25 @@ class PeerRegion:
         return regions
 
 
+def _mark(timers, name, fn):
+    """Runs fn(); with a timers list, brackets it with CUDA events on the current stream and appends (name, start, end)."""
+    if timers is None:
+        return fn()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    r = fn()
+    b.record()
+    timers.append((name, a, b))
+    return r
+
+
 class RouteState:
     """What a rank keeps between the stages of one call."""
     __slots__ = ("M", "ids", "inv_pos", "counts")
 
 
 def ep_route_stage(region: PeerRegion, hidden_states: torch.Tensor, gate: torch.Tensor, topk: int,
-                   num_experts: int, renormalize: bool = True) -> RouteState:
+                   num_experts: int, renormalize: bool = True, timers=None, copy_in: bool = True) -> RouteState:
     """Stage 1 (local): tokens into the region, fused router with the weights written straight into the region,
     align with block size 1 whose sorted list lands in the region.  Returns ids, positions and the histogram."""
     from .. import _lib
@@ -313,31 +325,34 @@ def ep_route_stage(region: PeerRegion, hidden_states: torch.Tensor, gate: torch.
     assert M <= region.rows and H == region.H and topk == region.topk and hidden_states.dtype == region.dtype
     n = M * topk
     dt = _lib.dtype_code(hidden_states.dtype)
-    region.x[:M].copy_(hidden_states)
+    if copy_in:
+        region.x[:M].copy_(hidden_states)
     st = RouteState()
     st.M = M
     st.ids = torch.empty(M, topk, dtype=torch.int32, device=dev)
     st.inv_pos = torch.empty(max(n, 1), dtype=torch.int32, device=dev)
     st.counts = torch.empty(E, dtype=torch.int32, device=dev)
     ws = _lib.workspace(lib.fr_route_fused_workspace_bytes(M, H, E, topk), dev, "route")
-    rc = lib.fr_route_fused(_lib.ptr(region.x), dt, M, H, region.x.stride(0), _lib.ptr(gate), gate.stride(0),
-                            gate.stride(1), E, topk, 1 if renormalize else 0, _lib.ptr(region.tw), _lib.ptr(st.ids),
-                            None, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+    rc = _mark(timers, "route", lambda: lib.fr_route_fused(
+        _lib.ptr(region.x), dt, M, H, region.x.stride(0), _lib.ptr(gate), gate.stride(0), gate.stride(1), E, topk,
+        1 if renormalize else 0, _lib.ptr(region.tw), _lib.ptr(st.ids), None, _lib.ptr(ws), ws.numel(),
+        _lib.stream_ptr(dev)))
     _lib.check(rc, "fr_route_fused")
     expert_of_row = _lib.workspace(4 * max(n, 1), dev, "ep_block1")      # block size 1: one entry per assignment
     num_post = torch.empty(1, dtype=torch.int32, device=dev)
     aws = _lib.workspace(lib.fr_align_workspace_bytes(E), dev, "align")
-    rc = lib.fr_align(_lib.ptr(st.ids), n, E, 1, _lib.ptr(region.sorted), n, _lib.ptr(expert_of_row), n,
-                      _lib.ptr(num_post), _lib.ptr(st.counts), _lib.ptr(st.inv_pos), _lib.ptr(aws), aws.numel(),
-                      _lib.stream_ptr(dev))
+    rc = _mark(timers, "moe_align", lambda: lib.fr_align(
+        _lib.ptr(st.ids), n, E, 1, _lib.ptr(region.sorted), n, _lib.ptr(expert_of_row), n, _lib.ptr(num_post),
+        _lib.ptr(st.counts), _lib.ptr(st.inv_pos), _lib.ptr(aws), aws.numel(), _lib.stream_ptr(dev)))
     _lib.check(rc, "fr_align")
     return st
 
 
 def ep_experts_stage(region: PeerRegion, rank: int, all_counts: torch.Tensor, w1_local: torch.Tensor,
-                     w2_local: torch.Tensor, num_experts: int, rows_hint: int = None) -> None:
+                     w2_local: torch.Tensor, num_experts: int, stages: int = 7) -> None:
     """Stage 2 (after every rank's stage 1 is visible): plan from the gathered histograms, gather of the token rows
-    from their owners, both grouped GEMMs; results stay in ``region.y``."""
+    from their owners, both grouped GEMMs; results stay in ``region.y``.  ``stages``: 1 = plan + gather, 2 = first
+    GEMM, 4 = second GEMM (a caller that times the stages issues them one by one)."""
     from .. import _lib
     lib = _lib.load()
     dev = w1_local.device
@@ -352,7 +367,7 @@ def ep_experts_stage(region: PeerRegion, rank: int, all_counts: torch.Tensor, w1
                            region.rows, region.sorted_off, region.tw_off, region.n, region.topk,
                            _lib.ptr(all_counts), _lib.ptr(w1_local), _lib.ptr(w2_local),
                            _lib.dtype_code(region.dtype), H, I, num_experts, _lib.ptr(region.y), region.y_rows,
-                           _lib.ptr(region.comb_base), _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+                           _lib.ptr(region.comb_base), stages, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
     _lib.check(rc, "fr_ep_experts")
 
 
@@ -412,19 +427,18 @@ def fused_moe_ep_p2p(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: 
     region = _peer_region(group, M, H, topk, hidden_states.dtype, dev)
 
     def mark(name, fn):
-        if timers is None:
-            return fn()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        r = fn()
-        b.record()
-        timers.append((name, a, b))
-        return r
+        return _mark(timers, name, fn)
 
-    st = mark("route+align", lambda: ep_route_stage(region, hidden_states, gate, topk, E, renormalize))
+    mark("copy into region", lambda: region.x[:M].copy_(hidden_states))
+    st = ep_route_stage(region, hidden_states, gate, topk, E, renormalize, timers, copy_in=False)
     all_counts = torch.empty(W, E, dtype=torch.int32, device=dev)
     mark("count all-gather", lambda: dist.all_gather_into_tensor(all_counts.view(-1), st.counts, group=group.pg))
-    mark("gather+experts", lambda: ep_experts_stage(region, group.rank, all_counts, w1_local, w2_local, E))
+    if timers is None:
+        ep_experts_stage(region, group.rank, all_counts, w1_local, w2_local, E)
+    else:
+        mark("gather", lambda: ep_experts_stage(region, group.rank, all_counts, w1_local, w2_local, E, 1))
+        mark("moe_1", lambda: ep_experts_stage(region, group.rank, all_counts, w1_local, w2_local, E, 2))
+        mark("moe_2", lambda: ep_experts_stage(region, group.rank, all_counts, w1_local, w2_local, E, 4))
     mark("results-ready sync", lambda: dist.all_reduce(region.sync_word, group=group.pg))
     return mark("combine", lambda: ep_combine_stage(region, st, E))
 

@@ -249,6 +249,8 @@ int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row
  *   expert-sorted operand -> GEMM1+SiLU -> GEMM2 x routing weight -> y_sorted (= this rank's y, y_rows rows,
  *   a multiple of 128; fr_moe_experts_rows_cap(world * n_per_rank, E / world) always suffices; more rows than
  *   that capacity are dropped and reported as status 4).  comb_base[E] is written for fr_ep_combine.
+ *   n_per_rank is the capacity of sorted / tw (and the row count the tile order is tuned for).  stages is a
+ *   mask: 1 = plan + gather, 2 = GEMM1, 4 = GEMM2 (7 = all; a caller timing the stages issues them one by one).
  * fr_ep_combine ("unpack"): out[t,:] = sum_j y of the owner of topk_ids[t,j], row comb_base[e] + inv_pos[t*k+j],
  *   fp32 in slot order; inv_pos is the one fr_align(block_size 1) returned on this rank.
  * The caller orders the ranks with two small collectives: every region's x / sorted / tw complete before any
@@ -258,7 +260,7 @@ size_t fr_ep_workspace_bytes(int64_t cap_rows, int H, int I, int E);
 int fr_ep_experts(const void* const* peer_base, int world, int rank, int64_t x_off, int64_t ld_x, int64_t peer_rows,
                   int64_t sorted_off, int64_t tw_off, int64_t n_per_rank, int topk, const int32_t* all_counts,
                   const void* w1, const void* w2, int dtype, int H, int I, int E, void* y_sorted, int64_t y_rows,
-                  int32_t* comb_base, void* workspace, size_t workspace_bytes, void* stream);
+                  int32_t* comb_base, int stages, void* workspace, size_t workspace_bytes, void* stream);
 int fr_ep_combine(const void* const* peer_base, int world, int64_t y_off, int64_t ld_y, int64_t y_rows, int dtype,
                   const int32_t* topk_ids, const int32_t* inv_pos, const int32_t* comb_base, int64_t M, int topk, int H,
                   int E, void* out, int64_t ld_out, void* stream);

@@ -22,7 +22,8 @@ def _free_port():
 
 def _rank_main(rank, world, port, M, H, I, E, k, skew, chunks, q, p2p=False):
     sys.path.insert(0, ROOT)
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0",
+                      TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     import datetime
     import torch.distributed as dist
     import fast_route_b200 as fr
@@ -92,20 +93,22 @@ def _run_ep(M, H, I, E, k, skew, chunks, exact, p2p):
         p.start()
     import queue
     import time
-    res, deadline = [], time.time() + 240
-    while len(res) < world:
+    res, deadline = [], time.time() + 300
+    failed = False
+    while len(res) < world and not failed:
         try:
             res.append(q.get(timeout=2))
         except queue.Empty:
-            dead = [p.exitcode for p in procs if p.exitcode not in (None, 0)]
-            if dead or time.time() > deadline:
-                for p in procs:
-                    if p.is_alive():
-                        p.kill()          # exact child processes started above
-                pytest.fail(f"a rank failed or timed out (exit codes {[p.exitcode for p in procs]})")
+            failed = any(p.exitcode not in (None, 0) for p in procs) or time.time() > deadline
+    # Ranks leave on their own: one that lost a peer gets an exception from its next collective when the process
+    # group's 120 s limit runs out, destroys its group and exits.  No child is killed (a rank ended with kernels
+    # or peer mappings live can disturb the GPUs of the others).
+    for p in procs:
+        p.join(timeout=200)
+    if failed or len(res) < world:
+        pytest.fail(f"a rank failed or timed out (exit codes {[p.exitcode for p in procs]})")
     res.sort()
     for p in procs:
-        p.join(timeout=60)
         assert p.exitcode == 0
     for rank, err, same, refmax in res:
         assert err == 0.0 if exact else err <= 2e-2 + refmax * 2.0 ** -7, (rank, err, refmax)

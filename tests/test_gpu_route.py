@@ -22,7 +22,7 @@ def bits(a):
     return np.ascontiguousarray(a).view(np.int32)
 
 
-@pytest.mark.parametrize("E,k", [(8, 2), (64, 6), (128, 8), (8, 8), (64, 2), (128, 2)])
+@pytest.mark.parametrize("E,k", [(8, 2), (8, 6), (8, 8), (64, 2), (64, 6), (64, 8), (128, 2), (128, 6), (128, 8)])
 def test_routing_microbench_bit_exact(dev, E, k):
     M, bs = 16384, 64
     logits = synth.routing_logits(M, E, k, seed=0, dtype=torch.float16, dup_frac=0.05)
@@ -148,6 +148,74 @@ def test_out_of_range_expert_id_is_reported_not_trapped(dev):
     assert code == 2 and count == 2
     assert int(npost.item()) == 12         # the three valid experts 0,1,2 still get their blocks
     assert _lib.device_status()[0] == 0    # reading clears
+
+
+@pytest.mark.reads_status
+def test_rejected_ids_contribute_zero_to_the_layer(dev):
+    """An id outside [0, E) (for instance -1 for "expert held elsewhere") is reported and its slot adds nothing:
+    the align stage marks its position -1, so the combine can never pick up a position an earlier call left in
+    the reused workspace.  Checked with the cooperative and the cluster align kernel, on the row-block, the
+    token-N and the split-K path, twice each."""
+    import fast_route_b200 as fr
+    from fast_route_b200 import _lib
+    _lib.device_status()
+    for M, H, I, E, k in ((5000, 256, 384, 8, 2), (3000, 256, 384, 8, 2), (200, 256, 384, 8, 2), (6, 512, 1024, 8, 2)):
+        x, gate, w1, w2 = synth.moe_inputs(M, H, I, E, seed=17, dtype=torch.bfloat16, weight_std=0.05)
+        xd, w1d, w2d = x.to(dev), w1.to(dev), w2.to(dev)
+        tw, ti = fr.fused_route(xd, gate.to(dev), k)
+        fr.fused_experts(xd, w1d, w2d, tw, ti)                      # fills the workspace with valid positions
+        bad = ti.clone()
+        bad[::3, 1] = -1
+        bad[1::7, 0] = E + 3
+        tw_masked = tw.clone()
+        tw_masked[::3, 1] = 0.0
+        tw_masked[1::7, 0] = 0.0
+        good = torch.where((bad < 0) | (bad >= E), torch.zeros_like(ti), bad)
+        want = fr.fused_experts(xd, w1d, w2d, tw_masked, good)      # same layer with the bad slots weighted zero
+        assert _lib.device_status()[0] == 0
+        for _ in range(2):
+            got = fr.fused_experts(xd, w1d, w2d, tw, bad)
+            code, _, _, count = _lib.device_status()
+            assert code == 2 and count >= int(((bad < 0) | (bad >= E)).sum())
+            assert torch.isfinite(got.float()).all()
+            assert (got.float() - want.float()).abs().max().item() <= 2e-2
+
+
+@pytest.mark.reads_status
+def test_grid_barrier_wait_runs_out_and_is_reported(dev):
+    """A bounded wait that expires: the count word of the align workspace's grid barrier is pre-set so that no
+    arrival can complete it, and the poll budget word next to it is set to a few thousand polls (milliseconds).
+    Every block must give up, the kernel must return, the status block must say 'wait expired', and after the
+    workspace has been zeroed again the next call must be bit-exact.  Nothing traps and nothing waits without
+    a limit."""
+    from fast_route_b200 import _lib
+    lib = _lib.load()
+    _lib.device_status()
+    M, k, E, bs = 16384, 2, 8, 64
+    n = M * k
+    g = torch.Generator().manual_seed(5)
+    ids = torch.randint(0, E, (M, k), generator=g, dtype=torch.int32)
+    idd = ids.to(dev)
+    s = torch.empty(n + E * (bs - 1), dtype=torch.int32, device=dev)
+    e = torch.empty(n + E, dtype=torch.int32, device=dev)
+    npost = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws = torch.zeros(lib.fr_align_workspace_bytes(E), dtype=torch.uint8, device=dev)
+
+    def call():
+        rc = lib.fr_align(_lib.ptr(idd), n, E, bs, _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(), _lib.ptr(npost),
+                          None, None, _lib.ptr(ws), ws.numel(), _lib.stream_ptr(dev))
+        assert rc == 0
+    words = ws[:16].view(torch.int32)
+    words[0] = 0x40000000           # arrivals can never reach "number of blocks - 1"
+    words[3] = 5000                 # polls before a block gives up
+    call()
+    code, detail, _, count = _lib.device_status()      # synchronises: the kernel returned
+    assert code == 1 and detail == 0x500 and count >= 1
+    ws.zero_()
+    call()
+    os_, oe, on, _ = oracle.moe_align_block_size(ids, bs, E)
+    assert _lib.device_status()[0] == 0
+    assert int(npost.item()) == int(on[0]) and np.array_equal(s.cpu().numpy(), os_)
 
 
 def _route_align_c_abi(dev, logits, k, bs, with_ws):

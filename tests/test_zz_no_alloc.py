@@ -54,6 +54,26 @@ def test_align_noalloc_matches_align_twice_in_a_row(dev, lib):
         assert np.array_equal(got[3].cpu().numpy(), oc)
 
 
+def test_align_noalloc_at_its_limits(dev, lib):
+    """The largest expert count and the largest batch the built-in array covers (8192 assignments per SM) still
+    match fr_align; one assignment more is refused with a clear error."""
+    import oracle
+    from fast_route_b200 import _lib
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    E, bs = 256, 16
+    n_max = 8192 * min(sms, 256)
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, E, (n_max,), generator=g, dtype=torch.int32)
+    got = _call_pair(lib, _lib, ids.to(dev), E, bs, dev)
+    os_, _, on, oc = oracle.moe_align_block_size(ids.view(-1, 1), bs, E)
+    assert np.array_equal(got[0].cpu().numpy(), os_) and int(got[2].item()) == int(on[0])
+    ids1 = torch.zeros(n_max + 1, dtype=torch.int32, device=dev)
+    s, e, npost, cnt, inv = _buffers(n_max + 1, E, bs, dev)
+    rc = lib.fr_align_noalloc(_lib.ptr(ids1), n_max + 1, E, bs, _lib.ptr(s), s.numel(), _lib.ptr(e), e.numel(),
+                              _lib.ptr(npost), _lib.ptr(cnt), _lib.ptr(inv), _lib.stream_ptr(dev))
+    assert rc == -2 and b"not supported" in lib.fr_error_string(rc)
+
+
 def test_align_noalloc_rejects_sizes_beyond_its_scratch(dev, lib):
     from fast_route_b200 import _lib
     E = 300                                     # more experts than the built-in array covers
