@@ -12,7 +12,7 @@ int topk_softmax_dispatch(const void* logits, int dtype, int64_t M, int E, int64
                           int64_t id_stride, int fill_rest, cudaStream_t st);
 int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                    int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                   int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st, int32_t* block_rows);
+                   int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st);
 size_t coop_workspace_bytes(int E);
 int align_noalloc_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids,
                            int64_t sorted_len, int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post,
@@ -21,8 +21,7 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st, int* deferred_split, const QuantArgs* quant, int64_t rows_hint,
-                          const int32_t* block_rows);
+                          cudaStream_t st, int* deferred_split, const QuantArgs* quant, int64_t rows_hint);
 int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid, int n_out, int64_t partial_cols,
                              const float* topk_w, const int32_t* inv_pos, int64_t M, int topk, int dtype,
                              const void* residual, int64_t ld_res, void* out, int64_t ld_out, cudaStream_t st);
@@ -637,7 +636,7 @@ static int route_fused_impl(const void* x, int dtype, int64_t M, int H, int64_t 
 }
 
 struct ExpertWs {
-  int32_t *sorted, *expert_ids, *num_post, *inv_pos, *counts, *block_rows;
+  int32_t *sorted, *expert_ids, *num_post, *inv_pos, *counts;
   uint16_t *a_sorted, *act, *y_sorted;
   void* split;
   void* align_ws;
@@ -662,7 +661,6 @@ static ExpertWs carve_experts(Carver& c, int64_t n, int H, int I, int E) {
   w.expert_ids_len = w.sorted_len / 16 + 1;   // block -> expert table, sized for the 16-row alignment
   w.sorted = c.take<int32_t>(w.sorted_len);
   w.expert_ids = c.take<int32_t>(w.expert_ids_len);
-  w.block_rows = c.take<int32_t>(w.expert_ids_len);
   w.num_post = c.take<int32_t>(4);
   w.inv_pos = c.take<int32_t>(n);
   w.counts = c.take<int32_t>(E);
@@ -732,8 +730,7 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
   const int row_v = H / 8;
   if (!prologue_done) {
     rc = align_dispatch(ids, n, E, tokenn ? 16 : kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
-                        w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st,
-                        tokenn ? nullptr : w.block_rows);
+                        w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
     if (rc) return rc;
     permute_rows_kernel<<<static_cast<unsigned>(w.rows), 256, 0, st>>>(
         static_cast<const uint4*>(x), ldx / 8, w.sorted, w.num_post, n, topk, reinterpret_cast<uint4*>(w.a_sorted),
@@ -753,15 +750,12 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
       return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + 127) / 128) * 128, weights,
                                       w.inv_pos, M, topk, dtype, residual, ld_res, out, ld_out, st);
   } else {
-    // block_rows: the last, partly filled 128-row block of every expert is multiplied with its tokens on the MMA N axis
     rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, w.rows, H, I, E, 2 * I, w.expert_ids, w.num_post,
-                               w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, nullptr, -1,
-                               w.block_rows);
+                               w.sorted, nullptr, n, w.act, I, w.sp.s1, w.split, w.sp.bytes, st, nullptr, nullptr);
     if (rc) return rc;
     int deferred = 0;
     rc = gemm_grouped_dispatch(1, w.act, I, w2, dtype, w.rows, I, H, E, H, w.expert_ids, w.num_post, w.sorted,
-                               weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred, nullptr, -1,
-                               w.block_rows);
+                               weights, n, w.y_sorted, H, w.sp.s2, w.split, w.sp.bytes, st, &deferred, nullptr);
     if (rc) return rc;
     if (deferred > 1)  // split-K GEMM2: its reduction, the routed weights and the sum over slots in one kernel
       return combine_partial_dispatch(w.split, deferred, n, H, static_cast<int64_t>((H + kTileN - 1) / kTileN) * kTileN,
@@ -781,7 +775,7 @@ static int experts_impl(const void* x, int64_t ldx, const int32_t* ids, const fl
 
 // ---- expert parallelism over peer memory (kernels in fr_ep.cu) ---------------------------------
 struct EpWs {
-  int32_t *seg_start, *seg_count, *seg_src_off, *num_post, *expert_ids, *sorted_local, *block_rows;
+  int32_t *seg_start, *seg_count, *seg_src_off, *num_post, *expert_ids, *sorted_local;
   float* w_sorted;
   uint16_t *a_sorted, *act;
 };
@@ -793,7 +787,6 @@ static EpWs carve_ep(Carver& c, int64_t cap_rows, int H, int I, int E) {
   w.seg_src_off = c.take<int32_t>(nseg);
   w.num_post = c.take<int32_t>(4);
   w.expert_ids = c.take<int32_t>(cap_rows / kBlockM + 1);
-  w.block_rows = c.take<int32_t>(cap_rows / kBlockM + 1);
   w.sorted_local = c.take<int32_t>(cap_rows);
   w.w_sorted = c.take<float>(cap_rows);
   w.a_sorted = c.take<uint16_t>(static_cast<size_t>(cap_rows) * H);
@@ -863,7 +856,7 @@ int fr_align(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t*
              int32_t* inv_pos, void* workspace, size_t workspace_bytes, void* stream) {
   return align_dispatch(topk_ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
                         num_tokens_post_pad, counts, inv_pos, workspace, workspace_bytes,
-                        static_cast<cudaStream_t>(stream), nullptr);
+                        static_cast<cudaStream_t>(stream));
 }
 
 int fr_align_noalloc(const int32_t* topk_ids, int64_t n, int E, int block_size, int32_t* sorted_ids,
@@ -888,7 +881,7 @@ int fr_route_align(const void* logits, int dtype, int64_t M, int E, int64_t stri
   int rc = topk_softmax_dispatch(logits, dtype, M, E, stride_m, stride_e, topk, 1, weights, topk, ids, topk, 0, st);
   if (rc) return rc;
   return align_dispatch(ids, n, E, block_size, sorted_ids, sorted_len, expert_ids, expert_ids_len,
-                        num_tokens_post_pad, nullptr, nullptr, workspace, workspace_bytes, st, nullptr);
+                        num_tokens_post_pad, nullptr, nullptr, workspace, workspace_bytes, st);
 }
 
 size_t fr_route_fused_workspace_bytes(int64_t M, int H, int E, int topk) {
@@ -966,7 +959,6 @@ int fr_ep_experts(const void* const* peer_base, int world, int rank, int64_t x_o
   pp.comb_base = comb_base;
   pp.num_post = w.num_post;
   pp.expert_ids = w.expert_ids;
-  pp.block_rows = w.block_rows;
   if (stages & 1) {
     ep_plan_kernel<<<1, 256, 0, st>>>(pp);
     FR_CUDA_OK(cudaGetLastError());
@@ -1007,12 +999,11 @@ int fr_ep_experts(const void* const* peer_base, int world, int rank, int64_t x_o
   if (stages & 2)
     rc = gemm_grouped_dispatch(0, w.a_sorted, H, w1, dtype, y_rows, H, I, El, 2 * I, w.expert_ids, w.num_post,
                                w.sorted_local, nullptr, y_rows, w.act, I, 1, nullptr, 0, st, nullptr, nullptr,
-                               rows_hint, w.block_rows);
+                               rows_hint);
   if (rc) return rc;
   if (stages & 4)
     rc = gemm_grouped_dispatch(1, w.act, I, w2, dtype, y_rows, I, H, El, H, w.expert_ids, w.num_post, w.sorted_local,
-                               w.w_sorted, y_rows, y_sorted, H, 1, nullptr, 0, st, nullptr, nullptr, rows_hint,
-                               w.block_rows);
+                               w.w_sorted, y_rows, y_sorted, H, 1, nullptr, 0, st, nullptr, nullptr, rows_hint);
   return rc;
 }
 
@@ -1288,7 +1279,7 @@ int fr_moe_layer_fp8(const void* x, const void* gate, int64_t gate_stride_h, int
   const int64_t n = M * topk;
   const bool tokenn = use_tokenn(n, E);
   rc = align_dispatch(ti, n, E, tokenn ? 16 : kBlockM, w.sorted, w.sorted_len, w.expert_ids, w.expert_ids_len,
-                      w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st, nullptr);
+                      w.num_post, w.counts, w.inv_pos, w.align_ws, w.align_ws_bytes, st);
   if (rc) return rc;
   const bool bf = dtype == FR_BF16;
   const unsigned rows = static_cast<unsigned>(w.rows);

@@ -37,7 +37,6 @@ struct EpPlanParams {
                           //     position of that assignment in this rank's sorted list
   int32_t* num_post;      // [1]
   int32_t* expert_ids;    // [cap_rows / 128] local expert of every 128-row block
-  int32_t* block_rows;    // [cap_rows / 128] rows of the block that hold tokens, rounded up to 16 (128 = full)
 };
 
 // One block.  E <= 1024, so every table fits in shared memory and the serial scans are a few hundred adds.
@@ -109,14 +108,8 @@ __global__ void __launch_bounds__(256) ep_plan_kernel(const EpPlanParams p) {
   }
   for (int j = 0; j < El; ++j) {
     const int b0 = start[lo + j] / kEpBlock;
-    const int bend = (start[lo + j] + (tot[lo + j] + kEpBlock - 1) / kEpBlock * kEpBlock) / kEpBlock;
-    const int b1 = min(num_post / kEpBlock, bend);
-    const int tail = tot[lo + j] % kEpBlock;
-    for (int b = b0 + threadIdx.x; b < b1; b += blockDim.x) {
-      p.expert_ids[b] = j;
-      // the expert's last block, when partly filled, is multiplied with its rows on the MMA N axis
-      p.block_rows[b] = (b == bend - 1 && tail) ? ((tail + 15) & ~15) : kEpBlock;
-    }
+    const int b1 = min(num_post, start[lo + j] + (tot[lo + j] + kEpBlock - 1) / kEpBlock * kEpBlock) / kEpBlock;
+    for (int b = b0 + threadIdx.x; b < b1; b += blockDim.x) p.expert_ids[b] = j;
   }
 }
 

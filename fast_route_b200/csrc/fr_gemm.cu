@@ -11,8 +11,6 @@
 // Thread roles in both kernels (192 threads): warp 0 = TMA producer (one lane),
 // warp 1 = TMEM owner + MMA issuer (one lane), warps 2..5 = epilogue (warp w reads the
 // TMEM lane quarter w % 4).  Every CTA loads its own operands.
-#include <cstdlib>
-
 #include "fr_common.cuh"
 
 namespace fr {
@@ -46,10 +44,6 @@ struct GemmParams {
   int group_m;
   const float* row_scale;  // fp8 inputs only: activation scale per sorted row
   const float* col_scale;  // fp8 inputs only: weight scale per weight row (E * b_rows_per_expert)
-  int debug;                  // measurement switches (bit 0: tail tiles skip their stores, bit 1: issue half the MMAs)
-  const int32_t* block_rows;  // per 128-row block: rows that hold tokens, rounded up to 16 (128 = full), or null.
-                              // With it, the last, partly filled row block of an expert is multiplied with the
-                              // tokens on the MMA N axis (N = that count) instead of as 128 padded rows.
 };
 
 struct PipeState {
@@ -156,15 +150,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     kb1 = min(KB, kb0 + p.kb_per_split);
   };
 
-  // Rows of block mb that carry tokens, rounded up to 16; BM for a full block (and whenever the table is absent).
-  auto block_rows = [&](int mb) -> int {
-    if constexpr (FP8 || MODE == MODE_PARTIAL) return BM;
-    if (!p.block_rows) return BM;
-    const int r = __ldg(p.block_rows + mb);
-    if (p.debug & 4) return r > 100000 ? r : BM;   // measurement: look the table up, treat every block as full
-    return (r >= 16 && r < BM && (r & 15) == 0) ? r : BM;
-  };
-
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
@@ -200,27 +185,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       PipeState ps;
       uint32_t it = 0;
       bool ok = true;
-      int rows_next = BM;   // fetched one tile ahead, so the table look-up never delays a tile's first MMA
-      if (static_cast<int>(blockIdx.x) < tiles) {
-        int mb, nb, kb0, kb1;
-        decode(blockIdx.x, mb, nb, kb0, kb1);
-        rows_next = block_rows(mb);
-      }
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++it) {
         int mb, nb, kb0, kb1;
         decode(tile, mb, nb, kb0, kb1);
-        const int rows16 = rows_next;
-        if (tile + static_cast<int>(gridDim.x) < tiles) {
-          int mb2, nb2, ka, kb;
-          decode(tile + gridDim.x, mb2, nb2, ka, kb);
-          rows_next = block_rows(mb2);
-        }
         const uint32_t buf = it & 1u, aphase = (it >> 1) & 1u;
         if (!wait_or_abort(&tempty[buf], aphase ^ 1, abort_flag, 0x200)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + buf * BN;
-        // partly filled block: D[128 weight rows, rows16 tokens] = W . X^T for each half of the B tile
-        const uint32_t idesc_t = umma_idesc_f16(BF16, BM, rows16);
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(&full[ps.stage], ps.phase, abort_flag, 0x201)) {
             ok = false;
@@ -229,20 +200,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           tc_fence_after();
           const uint64_t adesc = umma_desc_sw128(smem_u32(sA + ps.stage * A_STAGE_BYTES));
           const uint64_t bdesc = umma_desc_sw128(smem_u32(sB + ps.stage * SM::B_STAGE_BYTES));
-          if (rows16 == BM) {
 #pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {  // 4 MMAs per stage, 32 bytes of K each
-              if constexpr (FP8) tc_mma_f8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-              else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            }
-          } else {
-            constexpr uint64_t kHalfB = (static_cast<uint64_t>(BN / 2) * BK * 2) >> 4;  // second 128 weight rows
-#pragma unroll
-            for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint32_t acc = (kb > kb0 || k > 0) ? 1u : 0u;
-              tc_mma_f16(d_tmem, bdesc + 2 * k, adesc + 2 * k, idesc_t, acc);
-              if (!(p.debug & 2)) tc_mma_f16(d_tmem + BN / 2, bdesc + kHalfB + 2 * k, adesc + 2 * k, idesc_t, acc);
-            }
+          for (int k = 0; k < BK / UMMA_K; ++k) {  // 4 MMAs per stage, 32 bytes of K each
+            if constexpr (FP8) tc_mma_f8(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty[ps.stage]);  // frees the smem stage once these MMAs have read it
           ps.advance<STAGES>();
@@ -258,7 +219,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       int mb, nb, kb0, kb1;
       decode(tile, mb, nb, kb0, kb1);
       const uint32_t buf = it & 1u, aphase = (it >> 1) & 1u;
-      const int rows16 = block_rows(mb);   // issued before the wait: the look-up overlaps the tile's MMAs
       if (!wait_or_abort(&tfull[buf], aphase, abort_flag, 0x300)) break;
       tc_fence_after();
       const int64_t row = static_cast<int64_t>(mb) * BM + q * 32 + lane;
@@ -268,63 +228,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if constexpr (FP8) {
         rs = __ldg(p.row_scale + row);
         cs = p.col_scale + static_cast<int64_t>(__ldg(p.expert_ids + mb)) * p.b_rows_per_expert;
-      }
-      if (rows16 != BM) {
-        // Partly filled block: the accumulator is transposed (TMEM lane = weight row f of each B half, column =
-        // token), so this thread owns output feature f for every token and a warp stores 32 consecutive features
-        // of one token at a time (64 contiguous bytes).
-        if constexpr (!FP8 && MODE != MODE_PARTIAL) {
-          const int f = q * 32 + lane;
-          const int64_t row0 = static_cast<int64_t>(mb) * BM;
-          if constexpr (MODE == MODE_SILU) {
-            constexpr int HALF = BN / 2;
-            const int col = nb * HALF + f;
-            uint16_t* ocol = reinterpret_cast<uint16_t*>(p.out) + row0 * p.ldo + col;
-#pragma unroll 1
-            for (int c0 = 0; c0 < rows16; c0 += 16) {
-              uint32_t g[16], u[16];
-              tmem_ld16(taddr + c0, g);
-              tmem_ld16(taddr + HALF + c0, u);
-              tc_wait_ld();
-              if (col < p.n_out && !(p.debug & 1)) {
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                  const float v = silu_f(__uint_as_float(g[i])) * __uint_as_float(u[i]);
-                  ocol[static_cast<int64_t>(c0 + i) * p.ldo] = static_cast<uint16_t>(pack2<BF16>(v, 0.0f) & 0xFFFFu);
-                }
-              }
-            }
-          } else {
-            const int col0 = nb * BN + f, col1 = col0 + BN / 2;
-            uint16_t* ocol = reinterpret_cast<uint16_t*>(p.out) + row0 * p.ldo;
-#pragma unroll 1
-            for (int c0 = 0; c0 < rows16; c0 += 16) {
-              float wl = 0.0f;   // routing weight of token c0 + lane, held by lanes 0..15
-              if (lane < 16) {
-                const int32_t sid = __ldg(p.sorted_ids + row0 + c0 + lane);
-                if (sid >= 0 && sid < p.n_valid) wl = p.topk_w ? __ldg(p.topk_w + sid) : 1.0f;
-              }
-              uint32_t a0[16], a1[16];
-              tmem_ld16(taddr + c0, a0);
-              tmem_ld16(taddr + BN / 2 + c0, a1);
-              tc_wait_ld();
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const float w = __shfl_sync(0xffffffffu, wl, i);
-                uint16_t* orow = ocol + static_cast<int64_t>(c0 + i) * p.ldo;
-                if (p.debug & 1) continue;
-                if (col0 < p.n_out)
-                  orow[col0] = static_cast<uint16_t>(pack2<BF16>(w * __uint_as_float(a0[i]), 0.0f) & 0xFFFFu);
-                if (col1 < p.n_out)
-                  orow[col1] = static_cast<uint16_t>(pack2<BF16>(w * __uint_as_float(a1[i]), 0.0f) & 0xFFFFu);
-              }
-            }
-          }
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[buf]);
-        continue;
       }
 
       if constexpr (MODE == MODE_SILU) {
@@ -607,8 +510,7 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
                           int K, int n_out, int E, int b_rows_per_expert, const int32_t* expert_ids,
                           const int32_t* num_post, const int32_t* sorted_ids, const float* topk_w, int64_t n_valid,
                           void* out, int64_t ldo, int split_k, void* workspace, size_t workspace_bytes,
-                          cudaStream_t st, int* deferred_split, const QuantArgs* quant, int64_t rows_hint = -1,
-                          const int32_t* block_rows = nullptr) {
+                          cudaStream_t st, int* deferred_split, const QuantArgs* quant, int64_t rows_hint = -1) {
   // quant != nullptr: a and w hold E4M3 bytes (lda and K count elements = bytes), dtype is the output type.
   // which: 0 = GEMM1 (two-box B, SiLU epilogue), 1 = GEMM2 (weighted epilogue).
   // deferred_split (GEMM2 only, may be null): when split-K is used, skip the reduction and
@@ -643,10 +545,6 @@ int gemm_grouped_dispatch(int which, const void* a, int64_t lda, const void* w, 
   p.b_rows_per_expert = b_rows_per_expert;
   p.row_scale = fp8 ? quant->row_scale : nullptr;
   p.col_scale = fp8 ? quant->col_scale : nullptr;
-  static const int dbg = getenv("FR_TAIL_DEBUG") ? atoi(getenv("FR_TAIL_DEBUG")) : 0;
-  p.debug = dbg;
-  static const bool no_tail = getenv("FR_NO_TAIL_TILES") != nullptr;   // A/B switch for measurements
-  p.block_rows = no_tail ? nullptr : block_rows;
   p.two_box = (which == 0);
   p.b_half_offset = n_out;  // GEMM1: the linear ("up") branch starts I rows after the SiLU branch
   p.num_nb = p.two_box ? (n_out + GEMM_BN / 2 - 1) / (GEMM_BN / 2) : (n_out + GEMM_BN - 1) / GEMM_BN;

@@ -28,7 +28,7 @@ int launch_topk16(const void* logits, int64_t M, int E, int64_t stride_m, int64_
 int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                         int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
                         int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st,
-                        int64_t min_n = 8192, int32_t* block_rows = nullptr);
+                        int64_t min_n = 8192);
 
 __device__ __forceinline__ bool beats(float v, int c, float bv, int bc) {
   return (v > bv) || (v == bv && c < bc);
@@ -428,7 +428,6 @@ struct AlignParams {
   int32_t* inv_pos;
   int64_t seg;  // ids per warp, multiple of 32
   int nbits;    // bits needed for an expert id
-  int32_t* block_rows;  // optional, per block of bs rows: rows that hold tokens, rounded up to 16 (bs if full)
 };
 
 // ITERS > 0: a warp's slice is at most ITERS rows of 32 ids and is loaded once into
@@ -595,13 +594,7 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
     for (int q = s + t + lane; q < pe; q += 32)
       if (q < p.sorted_len) p.sorted[q] = static_cast<int32_t>(p.n);
     for (int blk = s / p.bs + lane; blk < pe / p.bs; blk += 32)
-      if (blk < p.expert_ids_len) {
-        p.expert_ids[blk] = e;
-        if (p.block_rows) {
-          const int tail = t % p.bs;
-          p.block_rows[blk] = (blk == pe / p.bs - 1 && tail) ? min(p.bs, (tail + 15) & ~15) : p.bs;
-        }
-      }
+      if (blk < p.expert_ids_len) p.expert_ids[blk] = e;
     if (p.counts && lane == 0) p.counts[e] = t;
   }
   const int64_t gthread = static_cast<int64_t>(rank) * blockDim.x + threadIdx.x;
@@ -613,8 +606,7 @@ __global__ void __launch_bounds__(1024) align_cluster_kernel(AlignParams p) {
 
 int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                    int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                   int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st,
-                   int32_t* block_rows = nullptr) {
+                   int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (!sorted_ids || !expert_ids || !num_post || n < 0 || E <= 0 || bs <= 0) return FR_ERR_ARG;
   if (n > 0 && !topk_ids) return FR_ERR_ARG;
   if (n >= (1ll << 30) || E > 2048) return FR_ERR_UNSUPPORTED;
@@ -625,7 +617,7 @@ int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* s
   // many assignments and a scratch buffer: spread over the whole GPU (one cooperative launch)
   {
     const int rc = align_coop_dispatch(topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len,
-                                       num_post, counts, inv_pos, workspace, workspace_bytes, st, 8192, block_rows);
+                                       num_post, counts, inv_pos, workspace, workspace_bytes, st);
     if (rc <= 0 && rc != FR_ERR_UNSUPPORTED) return rc;
     // a launch the device refused (cooperative grid too large for a partitioned GPU, ...) is not
     // fatal: clear the error and let the cluster kernel take the call
@@ -643,8 +635,7 @@ int align_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, int32_t* s
   seg = (seg + 31) / 32 * 32;
   if (seg == 0) seg = 32;
 
-  AlignParams p{topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post, counts, inv_pos, seg, 0,
-                block_rows};
+  AlignParams p{topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post, counts, inv_pos, seg, 0};
   while ((1 << p.nbits) < E) ++p.nbits;
   const size_t smem = (static_cast<size_t>(nwarps) * E + (4 + static_cast<size_t>(C)) * E + 1) * sizeof(int);
   if (smem > 200 * 1024) return FR_ERR_UNSUPPORTED;

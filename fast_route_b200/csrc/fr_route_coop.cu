@@ -257,7 +257,6 @@ struct CoopParams {
   int32_t* num_post;
   int32_t* counts;
   int32_t* inv_pos;
-  int32_t* block_rows;    // optional, per block of bs rows: rows that hold tokens, rounded up to 16 (bs if full)
   // scratch
   int32_t* hist;          // [gridDim][E]
   unsigned int* barrier;  // [2]
@@ -396,13 +395,7 @@ __device__ __forceinline__ void align_coop_body(const CoopParams& p, LoadIds&& l
     for (int q = s + t + lane; q < pe; q += 32)
       if (q < p.sorted_len) p.sorted[q] = static_cast<int32_t>(p.n);
     for (int blk = s / p.bs + lane; blk < pe / p.bs; blk += 32)
-      if (blk < p.expert_ids_len) {
-        p.expert_ids[blk] = e;
-        if (p.block_rows) {
-          const int tail = t % p.bs;
-          p.block_rows[blk] = (blk == pe / p.bs - 1 && tail) ? min(p.bs, (tail + 15) & ~15) : p.bs;
-        }
-      }
+      if (blk < p.expert_ids_len) p.expert_ids[blk] = e;
     if (p.counts && lane == 0) p.counts[e] = t;
   }
   const int64_t gthread = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -436,8 +429,7 @@ size_t coop_workspace_bytes(int E) {
 // cluster kernel.
 int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t* sorted_ids, int64_t sorted_len,
                         int32_t* expert_ids, int64_t expert_ids_len, int32_t* num_post, int32_t* counts,
-                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st, int64_t min_n,
-                        int32_t* block_rows) {
+                        int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st, int64_t min_n) {
   if (!workspace || workspace_bytes < coop_workspace_bytes(E) || (reinterpret_cast<uintptr_t>(workspace) & 15))
     return FR_ERR_UNSUPPORTED;
   if (n < min_n || n < 1 || E > 1024) return FR_ERR_UNSUPPORTED;
@@ -467,7 +459,6 @@ int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t
   p.num_post = num_post;
   p.counts = counts;
   p.inv_pos = inv_pos;
-  p.block_rows = block_rows;
   p.barrier = static_cast<unsigned int*>(workspace);
   p.hist = reinterpret_cast<int32_t*>(static_cast<uint8_t*>(workspace) + 256);
   p.per_block = per_block;
@@ -545,7 +536,7 @@ int align_noalloc_dispatch(const int32_t* topk_ids, int64_t n, int E, int bs, in
   // they are read.
   FR_CUDA_OK(cudaMemsetAsync(scratch, 0, 16, st));
   return align_coop_dispatch(topk_ids, n, E, bs, sorted_ids, sorted_len, expert_ids, expert_ids_len, num_post,
-                             counts, inv_pos, scratch, kNoAllocScratchBytes, st, /*min_n=*/1, nullptr);
+                             counts, inv_pos, scratch, kNoAllocScratchBytes, st, /*min_n=*/1);
 }
 
 }  // namespace fr

@@ -10,7 +10,7 @@ Per call, on every rank:
   2. local align with block size 1: a stable sort of the assignments by expert.  Experts
      are contiguous per rank, so the sorted order is already grouped by destination rank
      and the per-expert histogram gives the all-to-all split sizes;
-  3. a small all-to-all of the per-expert counts;
+  3. a small all-gather of the per-expert counts (every rank validates the same matrix);
   4. the permute kernel gathers token rows straight into the send buffer; NCCL all-to-all
      moves rows (and their routing weights) to the expert owners;
   5. the owner runs the expert pipeline on the received rows (align by local expert,
@@ -61,6 +61,25 @@ def exchange_counts(counts: torch.Tensor, group: ExpertParallelGroup) -> torch.T
     recv = torch.empty_like(send)
     dist.all_to_all_single(recv, send, group=group.pg)
     return recv
+
+
+def gather_counts(counts: torch.Tensor, group: ExpertParallelGroup) -> torch.Tensor:
+    """All-gather of the histograms: ``all_counts[W, E]``, identical on every rank, so that every rank validates the
+    same data and all of them accept or reject a step together (a rank that raised alone would leave its peers in
+    a collective that never completes)."""
+    out = torch.empty(group.world * counts.numel(), dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(out, counts.contiguous(), group=group.pg)
+    return out.view(group.world, -1)
+
+
+def validate_all_counts(all_counts: torch.Tensor, n_assignments: int) -> None:
+    """Rejects inconsistent histograms before any payload collective; same verdict on every rank."""
+    if int(all_counts.min()) < 0:
+        raise RuntimeError("negative row count in the gathered expert histograms")
+    sums = all_counts.sum(dim=1)
+    if int((sums != n_assignments).sum()):
+        bad = int((sums != n_assignments).nonzero()[0])
+        raise RuntimeError(f"expert histogram of rank {bad} sums to {int(sums[bad])}, expected {n_assignments}")
 
 
 def validate_counts(counts: torch.Tensor, n_assignments: int, recv_counts: torch.Tensor) -> None:
@@ -134,15 +153,18 @@ def fused_moe_ep(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: torc
         xc = hidden_states[lo:hi]
         tw, ti = fused_route(xc, gate, topk, renormalize=renormalize)
         sorted_ids, _, _, counts, inv_pos = fm.moe_align_block_size(ti, 1, E, return_extra=True)
-        st.append({"x": xc, "tw": tw, "sorted": sorted_ids, "inv": inv_pos, "counts": counts,
-                   "recv_counts": exchange_counts(counts, group), "n": (hi - lo) * topk})
+        allc = gather_counts(counts, group)            # [W, E], the same on every rank
+        elo, ehi = group.local_expert_range()
+        st.append({"x": xc, "tw": tw, "sorted": sorted_ids, "inv": inv_pos, "counts": counts, "all_counts": allc,
+                   "recv_counts": allc[:, elo:ehi].contiguous(), "n": (hi - lo) * topk})
     counts_h = torch.stack([c["counts"] for c in st]).cpu()
     recv_h = torch.stack([c["recv_counts"] for c in st]).cpu()
+    all_h = torch.stack([c["all_counts"] for c in st]).cpu()
 
     # stage 2: pack rows in destination order straight into the send buffer, start the dispatch
     for i, c in enumerate(st):
         n = c["n"]
-        validate_counts(counts_h[i], n, recv_h[i])
+        validate_all_counts(all_h[i], n)               # every rank sees the same matrix: all raise or none
         c["in_splits"] = send_splits(counts_h[i], group.world)
         c["out_splits"] = recv_h[i].sum(dim=1).tolist()
         num_post = torch.tensor([n], dtype=torch.int32, device=dev)

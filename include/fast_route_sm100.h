@@ -254,7 +254,8 @@ int fr_moe_experts(const void* rows, const int32_t* row_expert, const float* row
  * fr_ep_combine ("unpack"): out[t,:] = sum_j y of the owner of topk_ids[t,j], row comb_base[e] + inv_pos[t*k+j],
  *   fp32 in slot order; inv_pos is the one fr_align(block_size 1) returned on this rank.
  * The caller orders the ranks with two small collectives: every region's x / sorted / tw complete before any
- * fr_ep_experts (the all-gather of the counts does that), every y complete before any fr_ep_combine. */
+ * fr_ep_experts (the all-gather of the counts does that), every y complete before any fr_ep_combine.
+ * The workspace is fr_ep_workspace_bytes(y_rows, ...) bytes, 1024-byte aligned. */
 int64_t fr_moe_experts_rows_cap(int64_t R, int E_local);
 size_t fr_ep_workspace_bytes(int64_t cap_rows, int H, int I, int E);
 int fr_ep_experts(const void* const* peer_base, int world, int rank, int64_t x_off, int64_t ld_x, int64_t peer_rows,

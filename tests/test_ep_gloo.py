@@ -116,6 +116,43 @@ def test_ep_inconsistent_counts_rejected_before_payload():
     assert tags[1] == "rejected" and tags[0] == "ok-peer"
 
 
+def _reject_together_main(rank, world, port, out_q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+    sys.path.insert(0, ROOT)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        from fast_route_b200.parallel import ep
+        group = ep.ExpertParallelGroup(dist.group.WORLD, 4)
+        counts = torch.tensor([2, 2, 2, 2], dtype=torch.int32)
+        if rank == 1:
+            counts[0] += 1                               # only rank 1's histogram is inconsistent
+        allc = ep.gather_counts(counts, group)
+        try:
+            ep.validate_all_counts(allc, 8)
+            out_q.put((rank, "accepted"))
+        except RuntimeError as err:
+            out_q.put((rank, "rejected: " + str(err)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ep_inconsistent_counts_rejected_by_every_rank_together():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_reject_together_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = dict(q.get(timeout=60) for _ in range(world))
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert all(v.startswith("rejected") and "rank 1" in v for v in results.values()), results
+
+
 def test_ep_helpers():
     from fast_route_b200.parallel import ep
     rc = torch.tensor([[2, 0], [1, 3]], dtype=torch.int32)
@@ -123,6 +160,11 @@ def test_ep_helpers():
     assert ep.send_splits(torch.tensor([1, 2, 3, 4]), 2) == [3, 7]
     with pytest.raises(RuntimeError):
         ep.validate_counts(torch.tensor([1, 2]), 4, torch.tensor([[0]]))
+    ep.validate_all_counts(torch.tensor([[1, 3], [2, 2]]), 4)
+    with pytest.raises(RuntimeError, match="rank 1"):
+        ep.validate_all_counts(torch.tensor([[1, 3], [2, 3]]), 4)
+    with pytest.raises(RuntimeError):
+        ep.validate_all_counts(torch.tensor([[5, -1], [2, 2]]), 4)
 
 
 # ------------------------------------------------------------------------------------

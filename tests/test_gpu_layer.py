@@ -287,11 +287,12 @@ def test_mixtral_shape_at_every_benchmarked_batch_size(dev):
         diff = (out[rows].float() - ref).abs()
         assert (diff <= MAX_ABS + ref.abs() * 2.0 ** -7).all(), (M, diff.max().item())
         assert (diff.mean() / ref.abs().mean()).item() <= MEAN_REL, M
-        # The flat bound only fails where the output or one of the token's per-expert terms has magnitude >= 2: the
+        # The flat bound only fails where the output or one of the token's per-expert terms has magnitude >= 1: the
         # layer keeps those terms in bf16 before it sums them (as the reference keeps its third cache), neighbouring
-        # bf16 numbers are 2^-6 or more apart there, and 2e-2 is then less than 1.3 spacings of the format.
+        # bf16 numbers are 2^-7 or more apart there, and 2e-2 is then at most 2.6 spacings of the format, which three
+        # roundings (two terms, the sum) and the bf16 intermediate between the GEMMs can use up.
         over = diff > MAX_ABS
-        assert (_spacing_bf16(torch.maximum(slot_max, ref.abs())[over]) >= 2.0 ** -6).all()
+        assert (_spacing_bf16(torch.maximum(slot_max, ref.abs())[over]) >= 2.0 ** -7).all()
         total += diff.numel()
         inside += int((~over).sum())
         if M == 16384:
