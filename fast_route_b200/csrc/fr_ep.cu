@@ -138,44 +138,71 @@ __global__ void __launch_bounds__(256) ep_gather_kernel(const EpGatherParams p) 
   for (int i = threadIdx.x; i <= nseg; i += blockDim.x) seg_sm[i] = __ldg(p.seg_start + i);
   __syncthreads();
   const int num_post = seg_sm[nseg];
-  for (int64_t row = blockIdx.x; row < num_post; row += gridDim.x) {
-    // last segment whose start is <= row (empty segments share their start with the next one)
-    int lo = 0, hi = nseg - 1;
+  // Which source rank a row comes from and which of its assignments it is: a search in the segment table and one
+  // load from the source's sorted list.  Returns false for a padding row.
+  auto lookup = [&](int64_t row, int& s, int32_t& sid) -> bool {
+    int lo = 0, hi = nseg - 1;   // last segment whose start is <= row (empty segments share their start with the next)
     while (lo < hi) {
       const int mid = (lo + hi + 1) >> 1;
       if (seg_sm[mid] <= row) lo = mid; else hi = mid - 1;
     }
     const int off = static_cast<int>(row) - seg_sm[lo];
-    bool ok = off < __ldg(p.seg_count + lo);
-    int s = 0, token = 0;
-    float w = 0.0f;
-    if (ok) {
-      s = lo % p.W;
-      const int64_t q = static_cast<int64_t>(__ldg(p.seg_src_off + lo)) + off;
-      ok = q >= 0 && q < p.n_per_rank;
-      if (ok) {
-        const uint8_t* base = p.peer_base[s];
-        const int32_t sid = reinterpret_cast<const int32_t*>(base + p.sorted_off)[q];
-        ok = sid >= 0 && sid < p.n_per_rank;
-        if (ok) {
-          token = sid / p.topk;
-          w = reinterpret_cast<const float*>(base + p.tw_off)[sid];
-          ok = token < p.peer_rows;
-        }
-      }
-      if (!ok && threadIdx.x == 0) report(ST_BAD_SORTED_ID, static_cast<unsigned int>(row));
+    if (off >= __ldg(p.seg_count + lo)) return false;
+    s = lo % p.W;
+    const int64_t q = static_cast<int64_t>(__ldg(p.seg_src_off + lo)) + off;
+    if (q < 0 || q >= p.n_per_rank) {
+      sid = -1;
+      return true;
     }
+    sid = reinterpret_cast<const int32_t*>(p.peer_base[s] + p.sorted_off)[q];
+    return true;
+  };
+  int64_t row = blockIdx.x;
+  int s_cur = 0, s_nxt = 0;
+  int32_t sid_cur = -1, sid_nxt = -1;
+  bool real_cur = row < num_post && lookup(row, s_cur, sid_cur);
+  for (; row < num_post; row += gridDim.x) {
+    // the next row's look-up (a trip over NVLink) is issued now and consumed in the next iteration
+    const int64_t nrow = row + gridDim.x;
+    const bool real_nxt = nrow < num_post && lookup(nrow, s_nxt, sid_nxt);
+    bool ok = real_cur && sid_cur >= 0 && sid_cur < p.n_per_rank;
+    const int token = ok ? sid_cur / p.topk : 0;
+    ok = ok && token < p.peer_rows;
+    if (real_cur && !ok && threadIdx.x == 0) report(ST_BAD_SORTED_ID, static_cast<unsigned int>(row));
     uint4* d = p.a_sorted + row * p.ld_a_v;
     if (ok) {
-      const uint4* src = reinterpret_cast<const uint4*>(p.peer_base[s] + p.x_off) + static_cast<int64_t>(token) * p.ld_x_v;
-      for (int v = threadIdx.x; v < p.row_v; v += blockDim.x) d[v] = src[v];
+      const uint8_t* base = p.peer_base[s_cur];
+      const uint4* src = reinterpret_cast<const uint4*>(base + p.x_off) + static_cast<int64_t>(token) * p.ld_x_v;
+      float w = 0.0f;
+      if (threadIdx.x == 0) w = reinterpret_cast<const float*>(base + p.tw_off)[sid_cur];   // in flight with the row
+      // a row crosses NVLink with a latency of microseconds: keep four 16-byte loads per thread in flight
+      for (int v0 = threadIdx.x; v0 < p.row_v; v0 += 4 * blockDim.x) {
+        uint4 t[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * static_cast<int>(blockDim.x);
+          if (v < p.row_v) t[u] = src[v];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int v = v0 + u * static_cast<int>(blockDim.x);
+          if (v < p.row_v) d[v] = t[u];
+        }
+      }
+      if (threadIdx.x == 0) {
+        p.w_sorted[row] = w;
+        p.sorted_local[row] = static_cast<int32_t>(row);
+      }
     } else {
       for (int v = threadIdx.x; v < p.row_v; v += blockDim.x) d[v] = make_uint4(0, 0, 0, 0);
+      if (threadIdx.x == 0) {
+        p.w_sorted[row] = 0.0f;
+        p.sorted_local[row] = static_cast<int32_t>(p.cap_rows);
+      }
     }
-    if (threadIdx.x == 0) {
-      p.w_sorted[row] = ok ? w : 0.0f;
-      p.sorted_local[row] = ok ? static_cast<int32_t>(row) : static_cast<int32_t>(p.cap_rows);
-    }
+    real_cur = real_nxt;
+    s_cur = s_nxt;
+    sid_cur = sid_nxt;
   }
 }
 

@@ -111,5 +111,6 @@ def _run_ep(M, H, I, E, k, skew, chunks, exact, p2p):
     for p in procs:
         assert p.exitcode == 0
     for rank, err, same, refmax in res:
-        assert err == 0.0 if exact else err <= 2e-2 + refmax * 2.0 ** -7, (rank, err, refmax)
+        # not exact: other kernels on the two sides (router, split-K), so up to two bf16 spacings of the largest output
+        assert err == 0.0 if exact else err <= 2e-2 + refmax * 2.0 ** -6, (rank, err, refmax)
         assert same
