@@ -835,7 +835,7 @@ def run_ours(args, rank, world, local_rank):
                                                 "this size from a one-pass ncu capture (not measured in this run); "
                                                 "algorithmic bytes are 2.16 GB read (weights + A once) + 0.97 GB written")
         if not args.no_sweep and args.workload == "mixtral-8x7b":
-            Ms = [1, 4, 16, 64, 256, 1024, 2048, 4096, 8192, 16384]
+            Ms = [2 ** i for i in range(15)]          # the reference's sweep, benchmarks/fused_route/moe_bench.py:53
             line["sweep"] = sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms)
             line["stage_ms"] = stage_times_single_gpu(fr, wg, w1, w2, M, H, I, E, k)
             line["routing_latency"] = routing_latency(fr, synth, dev)
