@@ -380,6 +380,59 @@ __global__ void __launch_bounds__(256) router_small_kernel(const uint16_t* __res
                           logits_out);
 }
 
+// Logits of a handful of rows against MANY experts: the one-CTA-per-token router walks H once per 64 experts with
+// its loads in a serial chain (E = 128, H = 4096: 60 us for one token, whatever the batch).  Here a CTA takes 8
+// experts of one token and its 8 warps split H, so a token's experts spread over E / 8 CTAs; the ranking then runs
+// as the router-from-logits kernel on the fp32 logits.
+template <bool BF16>
+__global__ void __launch_bounds__(256) router_logits_small_kernel(const uint16_t* __restrict__ x, int64_t ldx,
+                                                                  const uint16_t* __restrict__ gate_km,
+                                                                  int64_t ld_gate, int H, int E,
+                                                                  float* __restrict__ logits_out) {
+  __shared__ float part[8][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int e0 = blockIdx.x * 8;
+  const int64_t row = blockIdx.y;
+  const uint16_t* xr = x + row * ldx;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int h = (warp * 32 + lane) * 8; h < H; h += 8 * 32 * 8) {
+    const uint4 xv = *reinterpret_cast<const uint4*>(xr + h);
+    const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+    uint4 gv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      gv[i] = (e0 + i < E) ? __ldg(reinterpret_cast<const uint4*>(gate_km + static_cast<int64_t>(e0 + i) * ld_gate + h))
+                           : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const uint32_t gw[4] = {gv[i].x, gv[i].y, gv[i].z, gv[i].w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 a = unpack2<BF16>(xw[q]);
+        const float2 b = unpack2<BF16>(gw[q]);
+        acc[i] = fmaf(a.x, b.x, acc[i]);
+        acc[i] = fmaf(a.y, b.y, acc[i]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float v = acc[i];
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    if (lane == 0) part[warp][i] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 8 && e0 + threadIdx.x < E) {
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) v += part[w][threadIdx.x];   // fixed order
+    if (v != v) v = -INFINITY;
+    logits_out[row * E + e0 + threadIdx.x] = v;
+  }
+}
+
 // Decode prologue: router, align (block 16) and the row gather of a batch of at most 16 assignments in ONE launch.
 // One CTA per token routes it; the CTA that finishes last (a counter in the zeroed scratch, put back to zero) then
 // sorts the handful of assignments by expert and copies the token rows into expert order.  At this size the three
@@ -498,8 +551,6 @@ __global__ void __launch_bounds__(256) decode_prologue_kernel(const ProloguePara
   }
 }
 
-constexpr int kSmallRouterRows = 32;
-
 // ----------------------------------------------------------------------------------
 // workspace carving
 // ----------------------------------------------------------------------------------
@@ -579,6 +630,14 @@ static SplitPlan plan_split_tokenn(int64_t n, int H, int I, int E) {
   return sp;
 }
 
+constexpr int kSmallRouterRows = 32;
+// The batches the one-CTA-per-token router takes (see route_fused_impl), and among them the ones with enough
+// experts that a token's experts are better spread over several CTAs.
+static bool small_router_batch(int64_t M, int H, int E) {
+  return M <= kSmallRouterRows || static_cast<int64_t>(M) * E * H < (int64_t(1) << 26);
+}
+static bool small_batch_many_experts(int64_t M, int H, int E) { return E >= 32 && E <= 1024 && small_router_batch(M, H, E); }
+
 struct RouteWs {
   uint16_t* gate_km;
   float* logits;
@@ -588,7 +647,8 @@ static RouteWs carve_route(Carver& c, int64_t M, int H, int E, int topk) {
   RouteWs r;
   r.ld_gate = round_up(H, 8);
   r.gate_km = c.take<uint16_t>(static_cast<size_t>(E) * r.ld_gate);
-  const bool need_logits = topk > 8;
+  // fp32 logits are kept when the ranking runs as its own kernel: topk > 8, or few rows against many experts
+  const bool need_logits = topk > 8 || small_batch_many_experts(M, H, E);
   r.logits = c.take<float>(need_logits ? static_cast<size_t>(M) * E : 0);
   return r;
 }
@@ -610,9 +670,23 @@ static int route_fused_impl(const void* x, int dtype, int64_t M, int H, int64_t 
   // one-CTA-per-token kernel also takes the mid-size batches for which its M*E*H multiply-adds cost less than that
   // (measured crossover: 2048 tokens at E = 8, H = 4096; 512 tokens at E = 64, H = 2048).  The two kernels add in
   // different orders, so the last bits of a token's logits depend on which one its batch size selects.
-  const bool gemv = M <= kSmallRouterRows || static_cast<int64_t>(M) * E * H < (int64_t(1) << 26);
-  if (gemv && (H % 8) == 0 && (ldx % 8) == 0 && (ld_gate % 8) == 0 && E <= 1024 &&
-      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(gate_km) & 15) == 0) {
+  const bool gemv = small_router_batch(M, H, E);
+  const bool vec_ok = (H % 8) == 0 && (ldx % 8) == 0 && (ld_gate % 8) == 0 &&
+                      (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(gate_km) & 15) == 0;
+  if (gemv && vec_ok && small_batch_many_experts(M, H, E) && (logits_out || ws.logits) && M <= 65535) {
+    float* lg = logits_out ? logits_out : ws.logits;
+    const dim3 grid(static_cast<unsigned>((E + 7) / 8), static_cast<unsigned>(M));
+    if (dtype == FR_BF16)
+      router_logits_small_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(x), ldx,
+                                                             static_cast<const uint16_t*>(gate_km), ld_gate, H, E, lg);
+    else
+      router_logits_small_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(x), ldx,
+                                                              static_cast<const uint16_t*>(gate_km), ld_gate, H, E, lg);
+    FR_CUDA_OK(cudaGetLastError());
+    if (!weights) return FR_OK;
+    return topk_softmax_dispatch(lg, FR_F32, M, E, E, 1, topk, renormalize, weights, topk, ids, topk, 0, st);
+  }
+  if (gemv && vec_ok && E <= 1024) {
     const size_t smem = static_cast<size_t>(10) * E * sizeof(float);
     if (dtype == FR_BF16)
       router_small_kernel<true><<<static_cast<unsigned>(M), 256, smem, st>>>(
@@ -682,7 +756,8 @@ static int decode_prologue_dispatch(const void* x, int dtype, int64_t M, int H, 
                                     int64_t gsh, int64_t gse, int E, int topk, int renormalize, float* weights,
                                     int32_t* ids, const ExpertWs& w, cudaStream_t st) {
   const int64_t n = M * topk;
-  if (n > kPrologueMaxAssign || M < 1 || !use_tokenn(n, E) || E > 1024 || !w.align_ws || w.align_ws_bytes < 16)
+  // (with many experts the router inside the prologue, one CTA per token, is the slow part: separate stages then)
+  if (n > kPrologueMaxAssign || M < 1 || !use_tokenn(n, E) || E >= 32 || !w.align_ws || w.align_ws_bytes < 16)
     return FR_ERR_UNSUPPORTED;
   if (dtype != FR_F16 && dtype != FR_BF16) return FR_ERR_UNSUPPORTED;
   // the gate must already be K-major (W_g[E,H] viewed as [H,E]); otherwise the transposing path runs
