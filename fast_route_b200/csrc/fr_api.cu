@@ -346,7 +346,7 @@ __device__ __forceinline__ void router_small_body(float* rs, int64_t row, const 
     int rank = 0;
     for (int o = 0; o < E; ++o) {
       const float ov = logit[o];
-      rank += (ov > v || (ov == v && o < c)) ? 1 : 0;
+      rank += static_cast<int>(ov > v) | (static_cast<int>(ov == v) & static_cast<int>(o < c));
     }
     byrank[rank] = v;
     if (rank < topk) ids[row * topk + rank] = c;

@@ -780,22 +780,21 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                   run_sum = run_sum * __expf(run_max - nm) + __expf(x - nm);
                   run_max = nm;
                 }
-                // shift-insert into the sorted top list; columns arrive in ascending
-                // order, so a strict compare keeps the lower expert id first on ties
-                float cv = x;
-                int cc = c;
-                bool carrying = false;
+                // Insert into the sorted top list.  An entry stays ahead of the newcomer if it is larger, or equal
+                // with a lower expert id (columns arrive in ascending order).  keep[j] is monotone in j; slot j
+                // keeps its entry, takes the newcomer (first slot that does not keep), or takes slot j-1's entry.
+                // All eight decisions are independent: no carry chain through the list.
+                bool keep[RKMAX];
 #pragma unroll
-                for (int j = 0; j < RKMAX; ++j) {
-                  const bool sw = carrying || cv > tv[j] || (cv == tv[j] && cc < tc[j]);
-                  const float t = tv[j];
-                  const int ti = tc[j];
-                  tv[j] = sw ? cv : t;
-                  tc[j] = sw ? cc : ti;
-                  cv = sw ? t : cv;
-                  cc = sw ? ti : cc;
-                  carrying = carrying || sw;
+                for (int j = 0; j < RKMAX; ++j)   // bitwise on purpose: no short-circuit branches (empty slots: -inf, INT_MAX)
+                  keep[j] = static_cast<bool>(static_cast<int>(tv[j] > x) | (static_cast<int>(tv[j] == x) & static_cast<int>(tc[j] < c)));
+#pragma unroll
+                for (int j = RKMAX - 1; j >= 1; --j) {
+                  tv[j] = keep[j] ? tv[j] : (keep[j - 1] ? x : tv[j - 1]);
+                  tc[j] = keep[j] ? tc[j] : (keep[j - 1] ? c : tc[j - 1]);
                 }
+                tv[0] = keep[0] ? tv[0] : x;
+                tc[0] = keep[0] ? tc[0] : c;
               }
             }
           }

@@ -30,8 +30,9 @@ int align_coop_dispatch(const int32_t* ids_in, int64_t n, int E, int bs, int32_t
                         int32_t* inv_pos, void* workspace, size_t workspace_bytes, cudaStream_t st,
                         int64_t min_n = 8192);
 
+// (bitwise on purpose: evaluated without short-circuit branches, which cost dearly inside unrolled selection loops)
 __device__ __forceinline__ bool beats(float v, int c, float bv, int bc) {
-  return (v > bv) || (v == bv && c < bc);
+  return static_cast<bool>(static_cast<int>(v > bv) | (static_cast<int>(v == bv) & static_cast<int>(c < bc)));
 }
 
 template <typename T, int L, int VPL>
