@@ -58,6 +58,14 @@ def test_argument_checks_reject_before_any_launch(lib):
     assert lib.fr_align(null, 8, 4, 16, null, 100, null, 100, null, null, null, null, 0, null) == -1
     assert lib.fr_moe_layer(null, null, 1, 1, null, null, 1, 4, 64, 64, 4, 2, 1, null, null, null, null, 0, null) == -1
     assert lib.fr_combine(null, 8, 1, null, 4, 2, 64, 128, null, 8, null) == -1
+    # expert-parallel entry points: null tables, experts that do not divide over the ranks, misaligned capacity
+    assert lib.fr_ep_experts(null, 2, 0, 0, 64, 8, 0, 0, 16, 2, null, null, null, 1, 64, 64, 8, null, 128, null, 7,
+                             null, 0, null) == -1
+    assert lib.fr_ep_combine(null, 2, 0, 64, 128, 1, null, null, null, 4, 2, 64, 8, null, 64, null) == -1
+    assert lib.fr_ep_workspace_bytes(0, 64, 64, 8) == 0
+    small, big = lib.fr_ep_workspace_bytes(1024, 4096, 14336, 8), lib.fr_ep_workspace_bytes(262272, 4096, 14336, 8)
+    assert 0 < small < big and big > 9 << 30      # the operand and the activations of 262272 rows: 9.7 GB
+    assert lib.fr_moe_experts_rows_cap(8 * 32768, 1) == 262272
 
 
 def test_product_never_imports_the_oracle():
