@@ -597,7 +597,6 @@ static SplitPlan plan_split(int64_t n, int H, int I, int E) {
   const int nb1 = (I + kTileN / 2 - 1) / (kTileN / 2), nb2 = (H + kTileN - 1) / kTileN;
   sp.s1 = choose_split_k(est_mb * nb1, (H + kTileK - 1) / kTileK, sms);
   sp.s2 = choose_split_k(est_mb * nb2, (I + kTileK - 1) / kTileK, sms);
-  if (const char* f = getenv("FR_FORCE_S2")) sp.s2 = atoi(f);   // measurement switch
   size_t b1 = sp.s1 > 1 ? static_cast<size_t>(sp.s1) * n * nb1 * kTileN * sizeof(float) : 0;
   size_t b2 = sp.s2 > 1 ? static_cast<size_t>(sp.s2) * n * nb2 * kTileN * sizeof(float) : 0;
   sp.bytes = b1 > b2 ? b1 : b2;
