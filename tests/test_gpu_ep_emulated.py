@@ -36,6 +36,7 @@ def _run_emulated(dev, W, M, H, I, E, k, skew, seed=7):
 
 @pytest.mark.parametrize("W,M,H,I,E,k,skew,exact", [(2, 4096, 2048, 1024, 8, 2, False, True),
                                                     (4, 2048, 4096, 512, 8, 2, False, True),
+                                                    (2, 8192, 4096, 512, 8, 2, False, True),
                                                     (8, 1024, 512, 768, 8, 2, False, False),
                                                     (4, 300, 256, 384, 16, 4, True, False),
                                                     (2, 3, 512, 1024, 8, 2, False, False),
