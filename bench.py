@@ -598,6 +598,10 @@ def config5_point(fr, ep, synth, group, world, rank, dev, dtype, peaks, steps, w
     layer, w1, w2, launches = make_layer(fr, ep, group, world, wg, w1_full, w2_full, k, ep_mode)
     g = torch.Generator(device=dev).manual_seed(500 + rank)
     xs = [torch.randn(M, H, device=dev, dtype=dtype, generator=g) for _ in range(2)]
+    if world > 1 and ep_mode == "p2p":            # tokens resident in the rank's peer region (see run_ours)
+        x0 = ep.peer_input(group, M, H, k, dtype, dev)
+        x0.copy_(xs[0])
+        xs = [x0, x0]
     ms = timed_layer_steps(layer, xs, steps, warmup, barrier, world, dist, dev)
     flops = synth.layer_flops(box_tokens, H, I, E, k)
     rep = {"workload": f"mixtral-8x22b MoE layer H={H} I={I} E={E} top-{k}, {box_tokens} tokens per box = {M} per rank, "
@@ -705,6 +709,13 @@ def run_ours(args, rank, world, local_rank):
 
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     xs = [torch.randn(M, H, device=dev, dtype=dtype, generator=g) for _ in range(3)]
+    if world > 1 and args.ep_mode == "p2p":
+        # device-resident tokens of an expert-parallel rank live where its peers can read them: the token buffer of
+        # the rank's peer region (one buffer, so every step reads the same batch; the weights, not the tokens, are
+        # what exceeds the L2)
+        x0 = ep.peer_input(group, M, H, k, dtype, dev)
+        x0.copy_(xs[0])
+        xs = [x0, x0, x0]
     if args.workload.endswith("-zipf"):
         wg[:, H - 1] = synth.zipf_gate_bias(E, 1.2, 1.6).to(device=dev, dtype=dtype)
         for xb in xs:

@@ -421,6 +421,14 @@ def _peer_region(group, M, H, topk, dtype, device) -> PeerRegion:
     return pr
 
 
+def peer_input(group: ExpertParallelGroup, M: int, H: int, topk: int, dtype, device) -> torch.Tensor:
+    """The ``[M,H]`` token buffer inside this rank's peer region (collective on first use, like the layer itself).
+    A caller that produces its tokens straight into it (the previous layer's output, a host-to-device copy) and
+    passes it to ``fused_moe_ep_p2p`` saves the copy into the region.  Write the next batch into it only on the
+    stream the layer calls are issued on: by then every peer has finished reading the previous one."""
+    return _peer_region(group, M, H, topk, dtype, torch.device(device)).x[:M]
+
+
 def fused_moe_ep_p2p(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: torch.Tensor,
                      w2_local: torch.Tensor, topk: int, group: ExpertParallelGroup,
                      renormalize: bool = True, timers=None) -> torch.Tensor:
@@ -451,7 +459,8 @@ def fused_moe_ep_p2p(hidden_states: torch.Tensor, gate: torch.Tensor, w1_local: 
     def mark(name, fn):
         return _mark(timers, name, fn)
 
-    mark("copy into region", lambda: region.x[:M].copy_(hidden_states))
+    if hidden_states.data_ptr() != region.x.data_ptr():       # tokens produced straight into the region need no copy
+        mark("copy into region", lambda: region.x[:M].copy_(hidden_states))
     st = ep_route_stage(region, hidden_states, gate, topk, E, renormalize, timers, copy_in=False)
     all_counts = torch.empty(W, E, dtype=torch.int32, device=dev)
     mark("count all-gather", lambda: dist.all_gather_into_tensor(all_counts.view(-1), st.counts, group=group.pg))

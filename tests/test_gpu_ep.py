@@ -43,7 +43,10 @@ def _rank_main(rank, world, port, M, H, I, E, k, skew, chunks, q, p2p=False):
         args = (x, gate.to(dev), w1[lo:hi].contiguous().to(dev), w2[lo:hi].contiguous().to(dev), k, group)
         if p2p:
             out = ep.fused_moe_ep_p2p(*args)
-            out2 = ep.fused_moe_ep_p2p(*args)
+            # second call with the tokens produced straight into the peer region (no copy inside the layer)
+            xin = ep.peer_input(group, x.shape[0], x.shape[1], k, x.dtype, dev)
+            xin.copy_(x)
+            out2 = ep.fused_moe_ep_p2p(xin, *args[1:])
         else:
             out = ep.fused_moe_ep(*args, chunks=chunks)
             out2 = ep.fused_moe_ep(*args, chunks=chunks)
