@@ -263,6 +263,41 @@ def test_plan_tables_small_example():
     assert p1["seg_start"].tolist() == [0, 5, 128, 130, 384] and p1["comb_base"].tolist() == [3, 127, 0, 125]
 
 
+def test_plan_tables_agree_between_token_owner_and_expert_owner():
+    """The invariant the peer-memory path rests on: from the same histogram matrix, the token owner's `comb_base`
+    and the expert owner's segment table name the same row for every assignment; segments of one owner are
+    disjoint, ordered and inside the padded extent of their expert."""
+    from fast_route_b200.parallel import ep
+    rng = np.random.default_rng(7)
+    for world, E in ((2, 8), (4, 8), (8, 8), (8, 64), (4, 12), (1, 4)):
+        for trial in range(6):
+            c = rng.integers(0, 400, size=(world, E))
+            c[rng.random((world, E)) < 0.2] = 0                     # experts a rank sends nothing to
+            if trial == 0:
+                c[:, 0] = 0                                          # an expert nobody uses
+            El = E // world
+            plans = [ep.plan_tables(c, r) for r in range(world)]
+            for owner in range(world):
+                po = plans[owner]
+                end_prev = 0
+                for j in range(El):
+                    e = owner * El + j
+                    tot = int(c[:, e].sum())
+                    first = int(po["seg_start"][j * world])
+                    assert first % 128 == 0 and first >= end_prev
+                    for s_ in range(world):
+                        i = j * world + s_
+                        assert int(po["seg_count"][i]) == c[s_, e]
+                        assert int(po["seg_src_off"][i]) == int(c[s_, :e].sum())
+                        assert int(po["seg_start"][i]) == first + int(c[:s_, e].sum())
+                        # the token owner s_ finds its assignments to e exactly there
+                        selfpre = int(c[s_, :e].sum())
+                        assert int(plans[s_]["comb_base"][e]) + selfpre == int(po["seg_start"][i])
+                    end_prev = first + (tot + 127) // 128 * 128
+                    assert (po["expert_ids"][first // 128:end_prev // 128] == j).all()
+                assert po["num_post"] == end_prev == int(po["seg_start"][El * world])
+
+
 # ------------------------------------------------------------------------------------
 # a peer that leaves between steps, a peer that never joins: the survivor gets an exception
 # ------------------------------------------------------------------------------------
