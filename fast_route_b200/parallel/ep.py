@@ -416,6 +416,11 @@ def _peer_region(group, M, H, topk, dtype, device) -> PeerRegion:
     key = (id(group.pg), H, topk, dtype, device.index)
     pr = _peer_state.get(key)
     if pr is None or pr.rows < M:
+        if pr is not None:
+            # growing: no peer may still be reading the old region when it is released (collective, like the
+            # allocation that follows)
+            torch.cuda.synchronize(device)
+            dist.barrier(group=group.pg)
         pr = PeerRegion(group, M, H, topk, dtype, device)
         _peer_state[key] = pr
     return pr
