@@ -42,6 +42,9 @@ def _rank_main(rank, world, port, M, H, I, E, k, skew, chunks, q, p2p=False):
         x = x_all[rank * M:(rank + 1) * M].contiguous().to(dev)
         args = (x, gate.to(dev), w1[lo:hi].contiguous().to(dev), w2[lo:hi].contiguous().to(dev), k, group)
         if p2p:
+            if x.shape[0] >= 4:      # a smaller batch first: the peer region then has to grow for the real one
+                half = x[:x.shape[0] // 2].contiguous()
+                ep.fused_moe_ep_p2p(half, *args[1:])
             out = ep.fused_moe_ep_p2p(*args)
             # second call with the tokens produced straight into the peer region (no copy inside the layer)
             xin = ep.peer_input(group, x.shape[0], x.shape[1], k, x.dtype, dev)
