@@ -8,17 +8,24 @@
 // B200 mapping.  The packed weights are streamed once, so weights sit on the MMA M axis (128 output columns per
 // CTA) and the few activation rows on the MMA N axis (16..128 per launch); a K step is 64 wide.
 // The K steps of a CTA are dealt round-robin to four independent pipelines ("groups"), each with its own input
-// stages, two operand tiles, an fp32 accumulator in TMEM and its own barriers:
+// stages, two operand buffers, an fp32 accumulator in TMEM and its own barriers:
 //   warp p (p = 0..3), one thread: TMA producer and MMA issuer of group p.  Loads the packed tile (8 words x 128
 //              columns, 4 KB) and the activation tile (m_pad rows x 64, 128-byte swizzle) of the group's steps, and
-//              issues tcgen05.mma (M=128, N=m_pad) on every operand tile the dequantisers hand over.
+//              issues tcgen05.mma (M=128, N=m_pad) on every operand the dequantisers hand over.
 //   warps 4+4p .. 7+4p: the 128 dequantisers of group p.  Thread t owns output column n0+t and expands the 8 packed
-//              words of a step into the 128-byte row t of a K-major, 128-byte-swizzled operand tile.
-// With so few activation rows an MMA is all issue latency (about 500 cycles for the four of a step), so one issuing
-// thread per CTA was the bottleneck; four pipelines that never wait for one another hide it.  The dequantising
-// warps drain the four accumulators at the end; warp 1 also allocates and frees TMEM.
-// The dequantisation is bound by instruction issue (about 2.5 instructions per weight for the exact fp16 recipe),
-// not by HBM.
+//              words of a step into 64 fp16 weights.  Up to 64 activation rows these go from registers straight into
+//              lane t of a tensor-memory buffer (tcgen05.st) and the MMA reads its A operand there; for larger
+//              batches, where the accumulators need the columns, into row t of a K-major, 128-byte-swizzled
+//              shared-memory tile.
+//   warp 20+p: helper of group p (tensor-memory mode): puts the activation tile into the k order of the weights.
+// In tensor-memory mode the weights are expanded with k interleaved inside every packed word (0, 4, 1, 5, 2, 6, 3,
+// 7), which takes one shift and four mask-or operations per word instead of four byte permutes; the activation tile
+// gets the same order in shared memory before the MMA reads it, and a sum over k does not care.
+// A thread can issue a tcgen05.mma only every hundred cycles or so, whatever its shape, so one issuing thread per
+// CTA was the bottleneck; four pipelines that never wait for one another hide it.  The dequantising warps drain the
+// four accumulators at the end; warp 1 also allocates and frees TMEM.
+// At these sizes the kernel is bound by the latency of one group's chain (barrier, packed words, expansion, store,
+// barrier, MMA issue, commit), not by HBM, the tensor pipe or the integer pipe.
 // Split-K runs as a thread-block cluster along K (1, 2, 4 or 8 CTAs): every CTA parks its fp32 partial tile in its
 // own shared memory, and after a cluster barrier CTA r sums rows r, r+S, ... over the ranks in rank order through
 // distributed shared memory.  No workspace, no atomics: the result does not depend on timing (the reference
@@ -41,7 +48,10 @@ constexpr int W4_RAW_BYTES = 8 * W4_BN * 4;     // 4 KB of packed words
 constexpr int W4_MAX_IN = 16;              // input ring depth (packed tile + activation tile)
 constexpr int W4_SMEM_BUDGET = 224 * 1024;
 constexpr int W4_MAX_M = 128;              // activation rows per launch (MMA N); larger batches run in chunks
-constexpr int W4_THREADS = 128 + W4_GROUPS * 128;
+constexpr int W4_HELPER_WARP0 = 4 + W4_GROUPS * 4;   // first of the four warps that reorder the activation tiles
+constexpr int W4_THREADS = 128 + W4_GROUPS * 128 + W4_GROUPS * 32;
+constexpr int W4_ATMEM_MAX_M = 64;         // up to this many rows the dequantised operand lives in tensor memory
+constexpr int W4_A_TMEM_COL0 = W4_GROUPS * W4_ATMEM_MAX_M;   // first column of the operand buffers
 
 
 struct W4Params {
@@ -69,6 +79,7 @@ struct W4Params {
 // Slow path (any other scale, zero and subnormal-prone ones included): integer nibbles -> fp16 -> multiply.
 struct W4Group {
   __half2 s2, zs2, mul2, add2;
+  __half2 s16_2, add1024_2, add64_2;
   bool fast;
   __device__ __forceinline__ void set(__half s, uint32_t z) {
     s2 = __half2half2(s);
@@ -76,10 +87,15 @@ struct W4Group {
     const unsigned short mag = __half_as_ushort(s) & 0x7FFFu;
     fast = mag >= 0x1800u && mag < 0x5000u;
     const __half s16 = __hmul_rn(s, __ushort_as_half(0x2C00));          // s / 16
+    const __half m1024 = __hneg(__hmul_rn(s, __ushort_as_half(0x6400)));     // -1024 s
+    const __half m64 = __hneg(__hmul_rn(s, __ushort_as_half(0x5400)));       // -64 s
     mul2 = __halves2half2(s, s16);
-    add2 = __halves2half2(__hneg(__hmul_rn(s, __ushort_as_half(0x6400))),      // -1024 s
-                          __hneg(__hmul_rn(s, __ushort_as_half(0x5400))));     // -64 s
+    add2 = __halves2half2(m1024, m64);
+    s16_2 = __half2half2(s16);
+    add1024_2 = __half2half2(m1024);
+    add64_2 = __half2half2(m64);
   }
+  // eight weights in memory order k = 0 .. 7
   template <bool FAST>
   __device__ __forceinline__ uint4 expand(uint32_t v) const {
     uint32_t out[4];
@@ -103,16 +119,62 @@ struct W4Group {
     }
     return make_uint4(out[0], out[1], out[2], out[3]);
   }
+  // The same eight weights in the order k = 0, 4, 1, 5, 2, 6, 3, 7: nibbles j and j + 4 sit 16 bits apart in the
+  // word, so a mask alone puts them into the two mantissas (nibbles 1, 3, 5, 7 land four bits up: 1024 + 16 q).
+  // One shift and four mask-or operations per word instead of four byte permutes and four mask-ors; the GEMM
+  // permutes the activation tile the same way, and a sum over k does not care about the order.
+  template <bool FAST>
+  __device__ __forceinline__ uint4 expand_interleaved(uint32_t v) const {
+    uint32_t out[4];
+    if constexpr (FAST) {
+      const uint32_t v8 = v >> 8;
+      const uint32_t b0 = (v & 0x000F000Fu) | 0x64006400u;      // 1024 + (q0, q4)
+      const uint32_t b1 = (v & 0x00F000F0u) | 0x64006400u;      // 1024 + 16 (q1, q5)
+      const uint32_t b2 = (v8 & 0x000F000Fu) | 0x64006400u;     // 1024 + (q2, q6)
+      const uint32_t b3 = (v8 & 0x00F000F0u) | 0x64006400u;     // 1024 + 16 (q3, q7)
+      __half2 q0 = __hsub2_rn(__hfma2(*reinterpret_cast<const __half2*>(&b0), s2, add1024_2), zs2);
+      __half2 q1 = __hsub2_rn(__hfma2(*reinterpret_cast<const __half2*>(&b1), s16_2, add64_2), zs2);
+      __half2 q2 = __hsub2_rn(__hfma2(*reinterpret_cast<const __half2*>(&b2), s2, add1024_2), zs2);
+      __half2 q3 = __hsub2_rn(__hfma2(*reinterpret_cast<const __half2*>(&b3), s16_2, add64_2), zs2);
+      out[0] = *reinterpret_cast<uint32_t*>(&q0);
+      out[1] = *reinterpret_cast<uint32_t*>(&q1);
+      out[2] = *reinterpret_cast<uint32_t*>(&q2);
+      out[3] = *reinterpret_cast<uint32_t*>(&q3);
+    } else {
+      const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t bits = 0x64006400u | ((v >> (4 * i)) & 0xFu) | (((v >> (4 * i + 16)) & 0xFu) << 16);
+        __half2 q = __hmul2_rn(__hsub2_rn(*reinterpret_cast<const __half2*>(&bits), k1024), s2);
+        q = __hsub2_rn(q, zs2);
+        out[i] = *reinterpret_cast<uint32_t*>(&q);
+      }
+    }
+    return make_uint4(out[0], out[1], out[2], out[3]);
+  }
   __device__ __forceinline__ uint4 expand_any(uint32_t v) const { return fast ? expand<true>(v) : expand<false>(v); }
 };
 
+// ATMEM (batches of up to 64 rows): the dequantised tile never touches shared memory.  Thread t writes its 64
+// weights (32 registers) into lane t of a 32-column tensor-memory buffer and the MMA takes its A operand from
+// there; columns [0, 256) hold the four accumulators, [256, 512) the four groups' two operand buffers.
+// Eight consecutive k of one activation row (a 16-byte chunk, wherever the swizzle put it) into the order the
+// weights are expanded in: k = 0, 4, 1, 5, 2, 6, 3, 7.
+__device__ __forceinline__ void permute_chunk(uint4* px) {
+  const uint4 x = *px;
+  *px = make_uint4(__byte_perm(x.x, x.z, 0x5410), __byte_perm(x.x, x.z, 0x7632), __byte_perm(x.y, x.w, 0x5410),
+                   __byte_perm(x.y, x.w, 0x7632));
+}
+
+template <bool ATMEM>
 __global__ void __launch_bounds__(W4_THREADS, 1)
 w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // layout: [W ring][X ring][packed ring][barriers]; the front of it doubles as the fp32 partial tile at the end
+  // layout: [W ring (not with ATMEM)][X ring][packed ring][barriers]; the front of it doubles as the fp32 partial
+  // tile at the end
   uint8_t* sW = smem;
-  uint8_t* sX = sW + W4_WSTAGES * W4_W_BYTES;
+  uint8_t* sX = sW + (ATMEM ? 0 : W4_WSTAGES * W4_W_BYTES);
   uint8_t* sQ = sX + p.in_stages * p.x_bytes;
   uint64_t* in_full = reinterpret_cast<uint64_t*>(sQ + p.in_stages * W4_RAW_BYTES);
   uint64_t* in_empty = in_full + W4_MAX_IN;
@@ -141,7 +203,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(&in_empty[s], 1);
     }
     for (int s = 0; s < W4_WSTAGES; ++s) {
-      mbar_init(&w_full[s], 4);      // the four warps of the owning group
+      mbar_init(&w_full[s], ATMEM ? 5 : 4);      // the four warps of the owning group (+ its helper warp)
       mbar_init(&w_empty[s], 1);
     }
     mbar_init(tfull, W4_GROUPS);     // one arrival per group, after its last MMA
@@ -202,11 +264,18 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           break;
         }
         tc_fence_after();
-        const uint64_t adesc = umma_desc_sw128(smem_u32(sW + (grp_id * W4_WBUFS + buf) * W4_W_BYTES));
         const uint64_t bdesc = umma_desc_sw128(smem_u32(sX + st * p.x_bytes));
+        if constexpr (ATMEM) {
+          const uint32_t a_tmem = tmem_base + W4_A_TMEM_COL0 + (grp_id * W4_WBUFS + buf) * (W4_BK / 2);
 #pragma unroll
-        for (int kk = 0; kk < W4_BK / 16; ++kk)
-          tc_mma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < W4_BK / 16; ++kk)
+            tc_mma_f16_a_tmem(d_tmem, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
+        } else {
+          const uint64_t adesc = umma_desc_sw128(smem_u32(sW + (grp_id * W4_WBUFS + buf) * W4_W_BYTES));
+#pragma unroll
+          for (int kk = 0; kk < W4_BK / 16; ++kk)
+            tc_mma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
+        }
         tc_commit(&my_w_empty[buf]);
         tc_commit(&in_empty[st]);
       }
@@ -214,7 +283,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (ok && own > 0) tc_commit(tfull);
       else mbar_arrive(tfull);
     }
-  } else {
+  } else if (warp < W4_HELPER_WARP0) {
     // ---------------- dequantise, then drain ----------------
     const int t = (threadIdx.x - 128) & 127;        // output column n0 + t, TMEM lane t
     const int grp_id = (threadIdx.x - 128) >> 7;    // owns steps grp_id, grp_id + 4, ...
@@ -229,12 +298,21 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     const int32_t* zp = p.qzeros + (n >> 3);
     const int zshift = (n & 7) * 4;
     // scale and zero point of the group's next step are loaded while it works on the current one
+    // (the quantisation group of a step advances by 4 / kpg, plus a carry, per own step: no division in the loop)
     __half s_next = __ushort_as_half(0);
     uint32_t z_next = 0;
-    if (n_ok && grp_id < nkb) {
-      const int g0 = ((kb_begin + grp_id) * W4_BK) / p.groupsize;
-      s_next = __ldg(sp + static_cast<int64_t>(g0) * p.n);
-      z_next = static_cast<uint32_t>(__ldg(zp + static_cast<int64_t>(g0) * (p.n >> 3)));
+    const int kpg = p.groupsize / W4_BK;              // K steps per quantisation group
+    const int g_adv = W4_GROUPS / kpg, g_rem_adv = W4_GROUPS % kpg;
+    int g_rem = 0;
+    if (grp_id < nkb) {
+      const int g0 = (kb_begin + grp_id) / kpg;
+      g_rem = (kb_begin + grp_id) % kpg;
+      sp += static_cast<int64_t>(g0) * p.n;
+      zp += static_cast<int64_t>(g0) * (p.n >> 3);
+      if (n_ok) {
+        s_next = __ldg(sp);
+        z_next = static_cast<uint32_t>(__ldg(zp));
+      }
     }
     bool ok = true;
     int st = grp_id;
@@ -242,36 +320,76 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     for (int i = grp_id; i < nkb; i += W4_GROUPS) {
       W4Group grp;
       grp.set(s_next, (z_next >> zshift) & 0xFu);
-      if (n_ok && i + W4_GROUPS < nkb) {
-        const int gn = ((kb_begin + i + W4_GROUPS) * W4_BK) / p.groupsize;
-        s_next = __ldg(sp + static_cast<int64_t>(gn) * p.n);
-        z_next = static_cast<uint32_t>(__ldg(zp + static_cast<int64_t>(gn) * (p.n >> 3)));
+      if (i + W4_GROUPS < nkb) {
+        g_rem += g_rem_adv;
+        const int carry = g_rem >= kpg ? 1 : 0;
+        g_rem -= carry ? kpg : 0;
+        sp += (g_adv + carry) * p.n;
+        zp += (g_adv + carry) * (p.n >> 3);
+        if (n_ok) {
+          s_next = __ldg(sp);
+          z_next = static_cast<uint32_t>(__ldg(zp));
+        }
       }
-      // the operand tile is free once the group's MMAs of two steps ago are complete
-      if (!wait_or_abort(&my_w_empty[buf], w_ph ^ 1, abort_flag, 0x821)) {
-        ok = false;
-        break;
-      }
-      if (!wait_or_abort(&in_full[st], in_ph, abort_flag, 0x820)) {
-        ok = false;
-        break;
+      // The operand buffer is free once the group's MMAs of two steps ago are complete, and the packed tile has
+      // usually landed: ask both barriers at once and only fall back to the bounded waits if one is not there yet.
+      {
+        const bool r1 = mbar_try_wait(&my_w_empty[buf], w_ph ^ 1), r2 = mbar_try_wait(&in_full[st], in_ph);
+        if (!(r1 && r2)) {
+          if (!wait_or_abort(&my_w_empty[buf], w_ph ^ 1, abort_flag, 0x821) ||
+              !wait_or_abort(&in_full[st], in_ph, abort_flag, 0x820)) {
+            ok = false;
+            break;
+          }
+        }
       }
       const uint32_t* q = reinterpret_cast<const uint32_t*>(sQ + st * W4_RAW_BYTES) + t;
-      uint8_t* wrow = w_base + buf * W4_W_BYTES + row_off;
       uint32_t words[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) words[j] = q[j * W4_BN];
-      if (grp.fast) {
+      if constexpr (ATMEM) {
+        // 64 weights of column t = 32 registers = lane t, 32 columns of the group's operand buffer; k interleaved
+        // inside every group of eight, the order the helper warp gives the activation tile
+        uint32_t regs[32];
+        if (grp.fast) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(wrow + ((j ^ (t & 7)) << 4)) = grp.expand<true>(words[j]);
+          for (int j = 0; j < 8; ++j) {
+            const uint4 w8 = grp.expand_interleaved<true>(words[j]);
+            regs[4 * j] = w8.x, regs[4 * j + 1] = w8.y, regs[4 * j + 2] = w8.z, regs[4 * j + 3] = w8.w;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 w8 = grp.expand_interleaved<false>(words[j]);
+            regs[4 * j] = w8.x, regs[4 * j + 1] = w8.y, regs[4 * j + 2] = w8.z, regs[4 * j + 3] = w8.w;
+          }
+        }
+        tc_fence_after();      // the buffer's last readers (MMAs) completed through w_empty
+        tmem_st32(tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + W4_A_TMEM_COL0 +
+                      (grp_id * W4_WBUFS + buf) * (W4_BK / 2), regs);
+        tc_wait_st();
+        tc_fence_before();
       } else {
+        // row t of the operand tile; chunk j goes to position j ^ (t & 7): one XOR on the shared-memory address
+        const uint32_t wrow = smem_u32(w_base + buf * W4_W_BYTES + row_off) ^ (static_cast<uint32_t>(t & 7) << 4);
+        if (grp.fast) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4*>(wrow + ((j ^ (t & 7)) << 4)) = grp.expand<false>(words[j]);
+          for (int j = 0; j < 8; ++j) {
+            const uint4 w8 = grp.expand<true>(words[j]);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wrow ^ (j << 4)), "r"(w8.x), "r"(w8.y),
+                         "r"(w8.z), "r"(w8.w) : "memory");
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const uint4 w8 = grp.expand<false>(words[j]);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wrow ^ (j << 4)), "r"(w8.x), "r"(w8.y),
+                         "r"(w8.z), "r"(w8.w) : "memory");
+          }
+        }
+        // make the generic-proxy writes visible to the tensor core (async proxy) before signalling
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
-      // make the generic-proxy writes visible to the tensor core (async proxy) before signalling
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&my_w_full[buf]);
       st += W4_GROUPS;
@@ -309,6 +427,33 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
       for (int i = 0; i < 16; ++i) partial[(c0 + i) * W4_BN + t] = acc[i];
     }
+  } else {
+    // ---------------- helper warp of a group: activation tiles into the weights' k order ----------------
+    if constexpr (ATMEM) {
+      const int grp_id = warp - W4_HELPER_WARP0;
+      uint64_t* my_w_full = w_full + grp_id * W4_WBUFS;
+      uint64_t* my_w_empty = w_empty + grp_id * W4_WBUFS;
+      int st = grp_id;
+      uint32_t in_ph = 0, buf = 0, w_ph = 0;
+      for (int i = grp_id; i < nkb; i += W4_GROUPS) {
+        // not ahead of the dequantisers: its arrival belongs to the same phase of w_full as theirs
+        if (!wait_or_abort(&my_w_empty[buf], w_ph ^ 1, abort_flag, 0x841)) break;
+        if (!wait_or_abort(&in_full[st], in_ph, abort_flag, 0x840)) break;
+        for (int ch = lane; ch < p.m_pad * 8; ch += 32) permute_chunk(reinterpret_cast<uint4*>(sX + st * p.x_bytes) + ch);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&my_w_full[buf]);
+        st += W4_GROUPS;
+        if (st >= in_stages) {
+          st -= in_stages;
+          in_ph ^= 1;
+        }
+        if (++buf == W4_WBUFS) {
+          buf = 0;
+          w_ph ^= 1;
+        }
+      }
+    }
   }
 
   // every CTA of the cluster has parked its partial tile
@@ -316,7 +461,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   cluster.sync();
 
-  if (warp >= 4) {
+  if (warp >= 4 && warp < W4_HELPER_WARP0) {
     const int t = (threadIdx.x - 128) & 127;
     const int grp_id = (threadIdx.x - 128) >> 7;
     const int n = n0 + t;
@@ -399,7 +544,6 @@ int w4a16_gemm_dispatch(const void* a, int64_t lda, const int32_t* qweight, cons
                         static_cast<uint64_t>(n) * 2, 8, 2 * W4_BN, false);
   if (rc) return rc;
 
-  auto kern = w4a16_gemm_kernel;
   for (int64_t m0 = 0; m0 < m; m0 += W4_MAX_M) {
     const int mc = static_cast<int>(m - m0 < W4_MAX_M ? m - m0 : W4_MAX_M);
     W4Params p = {};
@@ -413,25 +557,28 @@ int w4a16_gemm_dispatch(const void* a, int64_t lda, const int32_t* qweight, cons
     p.k = k;
     p.groupsize = groupsize;
     p.x_bytes = p.m_pad * 128;
-    int stages = (W4_SMEM_BUDGET - W4_WSTAGES * W4_W_BYTES) / (W4_RAW_BYTES + p.x_bytes);
+    const bool a_tmem = p.m_pad <= W4_ATMEM_MAX_M;
+    auto kern = a_tmem ? w4a16_gemm_kernel<true> : w4a16_gemm_kernel<false>;
+    const int w_ring = a_tmem ? 0 : W4_WSTAGES * W4_W_BYTES;
+    int stages = (W4_SMEM_BUDGET - w_ring) / (W4_RAW_BYTES + p.x_bytes);
     const int steps = (KB + S - 1) / S;
     if (stages > steps) stages = steps;
     if (stages > W4_MAX_IN) stages = W4_MAX_IN;
     // A multiple of the group count: the previous use of a stage then belongs to the same dequantising group,
     // which keeps every waiter within one phase of its barrier.
     p.in_stages = (stages + W4_GROUPS - 1) / W4_GROUPS * W4_GROUPS;
-    if ((W4_RAW_BYTES + p.x_bytes) * p.in_stages + W4_WSTAGES * W4_W_BYTES > W4_SMEM_BUDGET) p.in_stages -= W4_GROUPS;
+    if ((W4_RAW_BYTES + p.x_bytes) * p.in_stages + w_ring > W4_SMEM_BUDGET) p.in_stages -= W4_GROUPS;
     if (p.in_stages < W4_GROUPS) return FR_ERR_UNSUPPORTED;
     uint32_t cols = 32;
     while (cols < static_cast<uint32_t>(p.m_pad * W4_GROUPS)) cols *= 2;
-    p.tmem_cols = cols;
-    // the partial tile (m_pad x 128 fp32) reuses the operand ring and the start of the activation ring
-    if (p.m_pad * W4_BN * 4 > W4_WSTAGES * W4_W_BYTES + p.in_stages * p.x_bytes) return FR_ERR_UNSUPPORTED;
+    p.tmem_cols = a_tmem ? 512u : cols;
+    // the partial tile (m_pad x 128 fp32) reuses the front of the rings
+    if (p.m_pad * W4_BN * 4 > w_ring + p.in_stages * (p.x_bytes + W4_RAW_BYTES)) return FR_ERR_UNSUPPORTED;
     CUtensorMap tmX;
     rc = make_tmap_2d(&tmX, static_cast<const __half*>(a) + m0 * lda, static_cast<uint64_t>(mc),
                       static_cast<uint64_t>(k), static_cast<uint64_t>(lda), p.m_pad, 64, true);
     if (rc) return rc;
-    const int smem = W4_WSTAGES * W4_W_BYTES + p.in_stages * (p.x_bytes + W4_RAW_BYTES) + 512 + 1024;
+    const int smem = w_ring + p.in_stages * (p.x_bytes + W4_RAW_BYTES) + 512 + 1024;
     FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles, S, 1);
