@@ -73,6 +73,12 @@ def test_dequantised_weights_bit_exact(dev, k, n, gs):
     a[torch.arange(m), rows] = 1.0
     c = sk.matmul_split_k(a.to(dev), b.to(dev), s.to(dev), z.to(dev), gs)
     assert torch.equal(c.cpu(), w.cpu()[rows])
+    # up to 64 rows the kernel keeps the dequantised operand in tensor memory, with k interleaved inside every packed
+    # word and the activation tile reordered to match: the same exactness must hold there
+    for msmall in (1, 16, 48, 64):
+        msmall = min(msmall, m)
+        c = sk.matmul_split_k(a[:msmall].to(dev), b.to(dev), s.to(dev), z.to(dev), gs)
+        assert torch.equal(c.cpu(), w.cpu()[rows[:msmall]]), msmall
 
 
 @pytest.mark.parametrize("m", [1, 5, 16, 17, 100, 256, 300])
