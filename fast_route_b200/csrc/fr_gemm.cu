@@ -646,6 +646,11 @@ int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid
 // ==================================================================================
 // Fused router: one 128-row tile per CTA, N = padded expert count, whole K loop, then
 // each epilogue thread owns one row of logits in TMEM and selects its top-k in registers.
+// A thread can issue a tcgen05.mma only every hundred cycles or so, whatever its N, and
+// with so few columns that — not the tensor pipe — is what the K loop costs.  So for up
+// to 64 experts the K stages are dealt round-robin to four issuing threads on different
+// warps, each with its own accumulator; the epilogue adds the accumulators in a fixed
+// order.
 // ==================================================================================
 constexpr int RKMAX = 8;
 
@@ -663,17 +668,25 @@ struct RouterParams {
 
 template <int NPAD>
 struct RouterSmem {
-  static constexpr int STAGES = NPAD > 128 ? 4 : 6;  // 4 x 48 KB or 6 x <= 32 KB
+  // Several issuers pay while the K loop is the larger part: up to 64 experts.  Beyond that the epilogue (which
+  // also has every extra accumulator to read) outweighs it: measured 41 against 37 us at 128 experts, 2048 tokens.
+  static constexpr int ISSUERS = NPAD > 64 ? 1 : 4;
+  static constexpr int THREADS = 32 * (1 + ISSUERS + 4);  // producer, issuers, four epilogue warps
+  // A multiple of the issuer count, so that a stage is always consumed by the same issuer: a waiter then never
+  // lags its barrier by more than one phase (a parity wait cannot tell phase n from phase n + 2).
+  static constexpr int STAGES = NPAD > 128 ? 4 : (NPAD > 64 ? 6 : 8);   // 4 x 48 KB, 6 x 32 KB or 8 x <= 24 KB
+  static_assert(STAGES % ISSUERS == 0, "a stage belongs to one issuer");
   static constexpr int B_STAGE_BYTES = NPAD * BK * 2;
   static constexpr int TOTAL = STAGES * (A_STAGE_BYTES + (B_STAGE_BYTES < 1024 ? 1024 : B_STAGE_BYTES)) + 256 + 1024;
 };
 
 template <int NPAD, bool BF16>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(RouterSmem<NPAD>::THREADS, 1)
 router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmG,
                    const RouterParams p) {
   using SM = RouterSmem<NPAD>;
   constexpr int ROUTER_STAGES = SM::STAGES;
+  constexpr int NI = SM::ISSUERS;
   constexpr int B_STRIDE = SM::B_STAGE_BYTES < 1024 ? 1024 : SM::B_STAGE_BYTES;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -686,14 +699,14 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t TMEM_COLS = NPAD < 32 ? 32 : NPAD;
+  constexpr uint32_t TMEM_COLS = NI * NPAD < 32 ? 32 : NI * NPAD;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < ROUTER_STAGES; ++s) {
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], 1);
     }
-    mbar_init(tfull, 1);
+    mbar_init(tfull, NI);            // one arrival per issuer, after its last MMA
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&tmX);
@@ -721,26 +734,30 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         ps.advance<ROUTER_STAGES>();
       }
     }
-  } else if (warp == 1) {
+  } else if (warp <= NI) {
     if (lane == 0) {
+      // issuer i takes the K stages kb = i, i + NI, ... (always the same shared-memory stages) into accumulator i
+      const int issuer = warp - 1;
       constexpr uint32_t idesc = umma_idesc_f16(BF16, BM, NPAD);
-      PipeState ps;
+      const uint32_t d_tmem = tmem_base + issuer * NPAD;
       bool ok = true;
-      for (int kb = 0; kb < KB; ++kb) {
-        if (!wait_or_abort(&full[ps.stage], ps.phase, abort_flag, 0x401)) {
+      for (int kb = issuer; kb < KB; kb += NI) {
+        const int stage = kb % ROUTER_STAGES;
+        if (!wait_or_abort(&full[stage], static_cast<uint32_t>(kb / ROUTER_STAGES) & 1u, abort_flag, 0x401)) {
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint64_t adesc = umma_desc_sw128(smem_u32(sA + ps.stage * A_STAGE_BYTES));
-        const uint64_t bdesc = umma_desc_sw128(smem_u32(sB + ps.stage * B_STRIDE));
+        const uint64_t adesc = umma_desc_sw128(smem_u32(sA + stage * A_STAGE_BYTES));
+        const uint64_t bdesc = umma_desc_sw128(smem_u32(sB + stage * B_STRIDE));
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k)
-          tc_mma_f16(tmem_base, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-        tc_commit(&empty[ps.stage]);
-        ps.advance<ROUTER_STAGES>();
+          tc_mma_f16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb >= NI || k > 0) ? 1u : 0u);
+        tc_commit(&empty[stage]);
       }
-      if (ok) tc_commit(tfull);
+      // all of this issuer's MMAs (none, if it had no stage) are complete when this arrives
+      if (ok && issuer < KB) tc_commit(tfull);
+      else mbar_arrive(tfull);
     }
   } else {
     const int q = warp & 3;
@@ -757,11 +774,19 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         tc[j] = 0x7fffffff;
       }
       float run_max = -INFINITY, run_sum = 0.0f;
+      const int used = KB < NI ? KB : NI;       // accumulators that were written
 #pragma unroll 1
       for (int c0 = 0; c0 < NPAD; c0 += 16) {
         uint32_t a[16];
         tmem_ld16(taddr + c0, a);
         tc_wait_ld();
+        for (int acc = 1; acc < used; ++acc) {   // the issuers' partial sums, in issuer order
+          uint32_t b[16];
+          tmem_ld16(taddr + acc * NPAD + c0, b);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) a[i] = __float_as_uint(__fadd_rn(__uint_as_float(a[i]), __uint_as_float(b[i])));
+        }
         if (c0 < p.E) {
           if (p.logits && row_ok) {
 #pragma unroll
@@ -838,11 +863,11 @@ static int launch_router(const CUtensorMap& tmX, const CUtensorMap& tmG, const R
   if (bf) {
     auto kern = router_gemm_kernel<NPAD, true>;
     FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, 192, smem, st>>>(tmX, tmG, p);
+    kern<<<grid, RouterSmem<NPAD>::THREADS, smem, st>>>(tmX, tmG, p);
   } else {
     auto kern = router_gemm_kernel<NPAD, false>;
     FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    kern<<<grid, 192, smem, st>>>(tmX, tmG, p);
+    kern<<<grid, RouterSmem<NPAD>::THREADS, smem, st>>>(tmX, tmG, p);
   }
   return static_cast<int>(cudaGetLastError());
 }
