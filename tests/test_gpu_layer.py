@@ -35,7 +35,11 @@ def check_layer(out, ref):
 @pytest.mark.parametrize("M,H,E,k,dt", [(256, 512, 8, 2, torch.bfloat16), (300, 1024, 64, 6, torch.bfloat16),
                                         (128, 256, 128, 8, torch.float16), (1000, 4096, 8, 2, torch.bfloat16),
                                         (77, 192, 16, 4, torch.float16), (1, 4096, 8, 2, torch.bfloat16),
-                                        (513, 2048, 64, 12, torch.bfloat16), (4096, 1024, 200, 8, torch.float16)])
+                                        (513, 2048, 64, 12, torch.bfloat16), (4096, 1024, 200, 8, torch.float16),
+                                        # tensor-core router with four issuing threads (E <= 64, M*E*H >= 2^26) and
+                                        # fewer K stages than issuers / a stage count that is no multiple of four
+                                        (16384, 64, 64, 6, torch.bfloat16), (32768, 320, 8, 2, torch.float16),
+                                        (8192, 192, 48, 4, torch.bfloat16), (2048, 4096, 8, 2, torch.bfloat16)])
 def test_fused_route(dev, M, H, E, k, dt):
     x = synth.randn((M, H), 1, 0).to(dt)
     wg = synth.randn((E, H), 1, 1, 0.05).to(dt)
