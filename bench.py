@@ -465,6 +465,13 @@ def stage_times_single_gpu(fr, wg, w1, w2, M, H, I, E, k, reps=5):
     return {k_: round(v, 4) for k_, v in out.items()}
 
 
+def routing_latency_with_clocks(fr, synth, dev, device_index):
+    sampler = ClockSampler(device_index)
+    sampler.start()
+    rows = routing_latency(fr, synth, dev)
+    return {"rows": rows, "clocks": sampler.stop()}
+
+
 def router_from_hidden_states(fr, dev, dtype):
     """The reference's router op bench (benchmarks/fused_route/op_bench.py:62-130): fused_route from hidden
     states [m, 4096] to the top-k weights / ids, swept over the batch and the expert count."""
@@ -723,6 +730,13 @@ def run_ours(args, rank, world, local_rank):
                 args.ep_mode = "nccl"
     layer, w1, w2, launches_per_step = make_layer(fr, ep, group, world, wg, w1_full, w2_full, k, args.ep_mode)
 
+    # The routing microbenchmark is a latency measurement of two tiny kernels, so it scales with the SM clock and the
+    # clock depends on what ran before: it is taken here, before the GEMM loops push the GPU into its power cap, and
+    # once more after them (`routing_latency_after_load`), each with the clock sampled beside it.
+    routing_first = None
+    if world == 1 and not args.no_sweep and args.workload == "mixtral-8x7b":
+        routing_first = routing_latency_with_clocks(fr, synth, dev, local_rank)
+
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     xs = [torch.randn(M, H, device=dev, dtype=dtype, generator=g) for _ in range(3)]
     if world > 1 and args.ep_mode == "p2p":
@@ -873,7 +887,12 @@ def run_ours(args, rank, world, local_rank):
             Ms = [2 ** i for i in range(15)]          # the reference's sweep, benchmarks/fused_route/moe_bench.py:53
             line["sweep"] = sweep_single_gpu(fr, synth, wg, w1, w2, H, I, E, k, peaks, Ms)
             line["stage_ms"] = stage_times_single_gpu(fr, wg, w1, w2, M, H, I, E, k)
-            line["routing_latency"] = routing_latency(fr, synth, dev)
+            line["routing_latency"] = routing_first["rows"]
+            line["routing_latency_clocks"] = routing_first["clocks"]
+            after = routing_latency_with_clocks(fr, synth, dev, local_rank)
+            line["routing_latency_after_load"] = [
+                {k_: r[k_] for k_ in ("tokens", "E", "topk", "block", "us", "us_graph")} for r in after["rows"]]
+            line["routing_latency_after_load_clocks"] = after["clocks"]
             line["router_from_hidden_states"] = router_from_hidden_states(fr, dev, dtype)
             line["transformer_block"] = transformer_block(fr, wg, w1, w2, M, H, k)
             line["fp8_weights_mode"] = fp8_points(fr, synth, wg, w1, w2, H, I, E, k, peaks)
