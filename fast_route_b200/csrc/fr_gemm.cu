@@ -647,10 +647,10 @@ int combine_partial_dispatch(const void* workspace, int split_k, int64_t n_valid
 // Fused router: one 128-row tile per CTA, N = padded expert count, whole K loop, then
 // each epilogue thread owns one row of logits in TMEM and selects its top-k in registers.
 // A thread can issue a tcgen05.mma only every hundred cycles or so, whatever its N, and
-// with so few columns that — not the tensor pipe — is what the K loop costs.  So for up
-// to 64 experts the K stages are dealt round-robin to four issuing threads on different
-// warps, each with its own accumulator; the epilogue adds the accumulators in a fixed
-// order.
+// with so few columns that — not the tensor pipe — is what the K loop costs.  So up to
+// 128 experts the K stages are dealt round-robin to four (two) issuing threads on
+// different warps, each with its own accumulator; the epilogue adds the accumulators in
+// a fixed order.
 // ==================================================================================
 constexpr int RKMAX = 8;
 
@@ -668,9 +668,10 @@ struct RouterParams {
 
 template <int NPAD>
 struct RouterSmem {
-  // Several issuers pay while the K loop is the larger part: up to 64 experts.  Beyond that the epilogue (which
-  // also has every extra accumulator to read) outweighs it: measured 41 against 37 us at 128 experts, 2048 tokens.
-  static constexpr int ISSUERS = NPAD > 64 ? 1 : 4;
+  // Several issuers pay while the K loop is the larger part and the stages stay deep enough: four up to 64 experts
+  // (2048 tokens, 8 experts: 20.5 against 26.6 us), two at 128 (34.8 against 36.9 us; four, with one 32 KB stage each,
+  // 41 us), one at 256 (two: 53-55 against 51 us: the epilogue has every extra accumulator to read).
+  static constexpr int ISSUERS = NPAD > 128 ? 1 : (NPAD > 64 ? 2 : 4);
   static constexpr int THREADS = 32 * (1 + ISSUERS + 4);  // producer, issuers, four epilogue warps
   // A multiple of the issuer count, so that a stage is always consumed by the same issuer: a waiter then never
   // lags its barrier by more than one phase (a parity wait cannot tell phase n from phase n + 2).

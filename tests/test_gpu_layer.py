@@ -39,7 +39,9 @@ def check_layer(out, ref):
                                         # tensor-core router with four issuing threads (E <= 64, M*E*H >= 2^26) and
                                         # fewer K stages than issuers / a stage count that is no multiple of four
                                         (16384, 64, 64, 6, torch.bfloat16), (32768, 320, 8, 2, torch.float16),
-                                        (8192, 192, 48, 4, torch.bfloat16), (2048, 4096, 8, 2, torch.bfloat16)])
+                                        (8192, 192, 48, 4, torch.bfloat16), (2048, 4096, 8, 2, torch.bfloat16),
+                                        # ... and with two issuing threads (65 to 128 experts)
+                                        (4096, 1024, 128, 8, torch.bfloat16), (4096, 320, 100, 8, torch.float16)])
 def test_fused_route(dev, M, H, E, k, dt):
     x = synth.randn((M, H), 1, 0).to(dt)
     wg = synth.randn((E, H), 1, 1, 0.05).to(dt)
