@@ -734,7 +734,7 @@ def run_ours(args, rank, world, local_rank):
     # clock depends on what ran before: it is taken here, before the GEMM loops push the GPU into its power cap, and
     # once more after them (`routing_latency_after_load`), each with the clock sampled beside it.
     routing_first = None
-    if world == 1 and not args.no_sweep and args.workload == "mixtral-8x7b":
+    if world == 1 and not args.no_sweep and not args.profile and args.workload == "mixtral-8x7b":
         routing_first = routing_latency_with_clocks(fr, synth, dev, local_rank)
 
     g = torch.Generator(device=dev).manual_seed(100 + rank)
