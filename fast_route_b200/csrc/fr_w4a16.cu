@@ -8,24 +8,26 @@
 // B200 mapping.  The packed weights are streamed once, so weights sit on the MMA M axis (128 output columns per
 // CTA) and the few activation rows on the MMA N axis (16..128 per launch); a K step is 64 wide.
 // The K steps of a CTA are dealt round-robin to four independent pipelines ("groups"), each with its own input
-// stages, two operand buffers, an fp32 accumulator in TMEM and its own barriers:
+// stages, operand buffers, an fp32 accumulator in TMEM and its own barriers:
 //   warp p (p = 0..3), one thread: TMA producer and MMA issuer of group p.  Loads the packed tile (8 words x 128
-//              columns, 4 KB) and the activation tile (m_pad rows x 64, 128-byte swizzle) of the group's steps, and
-//              issues tcgen05.mma (M=128, N=m_pad) on every operand the dequantisers hand over.
+//              columns per step, 4 KB) and the activation tile (m_pad rows x 64, 128-byte swizzle) of the group's
+//              steps, and issues tcgen05.mma (M=128, N=m_pad) on every operand the dequantisers hand over.
 //   warps 4+4p .. 7+4p: the 128 dequantisers of group p.  Thread t owns output column n0+t and expands the 8 packed
-//              words of a step into 64 fp16 weights.  Up to 64 activation rows these go from registers straight into
-//              lane t of a tensor-memory buffer (tcgen05.st) and the MMA reads its A operand there; for larger
-//              batches, where the accumulators need the columns, into row t of a K-major, 128-byte-swizzled
-//              shared-memory tile.
-//   warp 20+p: helper of group p (tensor-memory mode): puts the activation tile into the k order of the weights.
-// In tensor-memory mode the weights are expanded with k interleaved inside every packed word (0, 4, 1, 5, 2, 6, 3,
-// 7), which takes one shift and four mask-or operations per word instead of four byte permutes; the activation tile
-// gets the same order in shared memory before the MMA reads it, and a sum over k does not care.
+//              words of a step into 64 fp16 weights.
+// Two kernels share this frame:
+//   w4a16_gemm_pair_kernel (up to 64 activation rows): the weights go from registers straight into lane t of a
+//              tensor-memory buffer (tcgen05.st) and the MMA reads its A operand there; a round of a group is two
+//              consecutive K steps; the eight weights of a packed word come out with k interleaved (0, 4, 1, 5, 2, 6,
+//              3, 7: one shift and four mask-or operations per word instead of four byte permutes) and a helper warp
+//              per group (warps 20..23) gives the activation tile the same order in shared memory before the MMA
+//              reads it (a sum over k does not care about the order).
+//   w4a16_gemm_smem_kernel (65 to 128 rows, where the accumulators need the tensor-memory columns): the weights go
+//              into row t of a K-major, 128-byte-swizzled shared-memory tile, natural k order, one K step per round.
 // A thread can issue a tcgen05.mma only every hundred cycles or so, whatever its shape, so one issuing thread per
 // CTA was the bottleneck; four pipelines that never wait for one another hide it.  The dequantising warps drain the
 // four accumulators at the end; warp 1 also allocates and frees TMEM.
-// At these sizes the kernel is bound by the latency of one group's chain (barrier, packed words, expansion, store,
-// barrier, MMA issue, commit), not by HBM, the tensor pipe or the integer pipe.
+// At these sizes the kernels are bound by instruction issue, most of it the bookkeeping of a round (scale and zero
+// point, addresses, barrier polls, fences, the arrive) rather than the expansion itself, not by HBM or the tensor pipe.
 // Split-K runs as a thread-block cluster along K (1, 2, 4 or 8 CTAs): every CTA parks its fp32 partial tile in its
 // own shared memory, and after a cluster barrier CTA r sums rows r, r+S, ... over the ranks in rank order through
 // distributed shared memory.  No workspace, no atomics: the result does not depend on timing (the reference
@@ -50,8 +52,8 @@ constexpr int W4_SMEM_BUDGET = 224 * 1024;
 constexpr int W4_MAX_M = 128;              // activation rows per launch (MMA N); larger batches run in chunks
 constexpr int W4_HELPER_WARP0 = 4 + W4_GROUPS * 4;   // first of the four warps that reorder the activation tiles
 constexpr int W4_THREADS = 128 + W4_GROUPS * 128 + W4_GROUPS * 32;
+constexpr int W4_THREADS_SMEM = 128 + W4_GROUPS * 128;          // the shared-memory-operand kernel has no helper warps
 constexpr int W4_ATMEM_MAX_M = 64;         // up to this many rows the dequantised operand lives in tensor memory
-constexpr int W4_A_TMEM_COL0 = W4_GROUPS * W4_ATMEM_MAX_M;   // first column of the operand buffers
 
 
 struct W4Params {
@@ -155,26 +157,15 @@ struct W4Group {
   __device__ __forceinline__ uint4 expand_any(uint32_t v) const { return fast ? expand<true>(v) : expand<false>(v); }
 };
 
-// ATMEM (batches of up to 64 rows): the dequantised tile never touches shared memory.  Thread t writes its 64
-// weights (32 registers) into lane t of a 32-column tensor-memory buffer and the MMA takes its A operand from
-// there; columns [0, 256) hold the four accumulators, [256, 512) the four groups' two operand buffers.
-// Eight consecutive k of one activation row (a 16-byte chunk, wherever the swizzle put it) into the order the
-// weights are expanded in: k = 0, 4, 1, 5, 2, 6, 3, 7.
-__device__ __forceinline__ void permute_chunk(uint4* px) {
-  const uint4 x = *px;
-  *px = make_uint4(__byte_perm(x.x, x.z, 0x5410), __byte_perm(x.x, x.z, 0x7632), __byte_perm(x.y, x.w, 0x5410),
-                   __byte_perm(x.y, x.w, 0x7632));
-}
-
-template <bool ATMEM>
-__global__ void __launch_bounds__(W4_THREADS, 1)
-w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
+// Batches of more than 64 rows (the accumulators then need the tensor-memory columns): the dequantised operand goes
+// through shared memory, one K step per round, weights in natural k order.
+__global__ void __launch_bounds__(W4_THREADS_SMEM, 1)
+w4a16_gemm_smem_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // layout: [W ring (not with ATMEM)][X ring][packed ring][barriers]; the front of it doubles as the fp32 partial
-  // tile at the end
+  // layout: [W ring][X ring][packed ring][barriers]; the front of it doubles as the fp32 partial tile at the end
   uint8_t* sW = smem;
-  uint8_t* sX = sW + (ATMEM ? 0 : W4_WSTAGES * W4_W_BYTES);
+  uint8_t* sX = sW + W4_WSTAGES * W4_W_BYTES;
   uint8_t* sQ = sX + p.in_stages * p.x_bytes;
   uint64_t* in_full = reinterpret_cast<uint64_t*>(sQ + p.in_stages * W4_RAW_BYTES);
   uint64_t* in_empty = in_full + W4_MAX_IN;
@@ -203,7 +194,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       mbar_init(&in_empty[s], 1);
     }
     for (int s = 0; s < W4_WSTAGES; ++s) {
-      mbar_init(&w_full[s], ATMEM ? 5 : 4);      // the four warps of the owning group (+ its helper warp)
+      mbar_init(&w_full[s], 4);      // the four warps of the owning group
       mbar_init(&w_empty[s], 1);
     }
     mbar_init(tfull, W4_GROUPS);     // one arrival per group, after its last MMA
@@ -265,17 +256,10 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         }
         tc_fence_after();
         const uint64_t bdesc = umma_desc_sw128(smem_u32(sX + st * p.x_bytes));
-        if constexpr (ATMEM) {
-          const uint32_t a_tmem = tmem_base + W4_A_TMEM_COL0 + (grp_id * W4_WBUFS + buf) * (W4_BK / 2);
+        const uint64_t adesc = umma_desc_sw128(smem_u32(sW + (grp_id * W4_WBUFS + buf) * W4_W_BYTES));
 #pragma unroll
-          for (int kk = 0; kk < W4_BK / 16; ++kk)
-            tc_mma_f16_a_tmem(d_tmem, a_tmem + 8 * kk, bdesc + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
-        } else {
-          const uint64_t adesc = umma_desc_sw128(smem_u32(sW + (grp_id * W4_WBUFS + buf) * W4_W_BYTES));
-#pragma unroll
-          for (int kk = 0; kk < W4_BK / 16; ++kk)
-            tc_mma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < W4_BK / 16; ++kk)
+          tc_mma_f16(d_tmem, adesc + 2 * kk, bdesc + 2 * kk, idesc, (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&my_w_empty[buf]);
         tc_commit(&in_empty[st]);
       }
@@ -283,7 +267,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       if (ok && own > 0) tc_commit(tfull);
       else mbar_arrive(tfull);
     }
-  } else if (warp < W4_HELPER_WARP0) {
+  } else {
     // ---------------- dequantise, then drain ----------------
     const int t = (threadIdx.x - 128) & 127;        // output column n0 + t, TMEM lane t
     const int grp_id = (threadIdx.x - 128) >> 7;    // owns steps grp_id, grp_id + 4, ...
@@ -347,49 +331,25 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       uint32_t words[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) words[j] = q[j * W4_BN];
-      if constexpr (ATMEM) {
-        // 64 weights of column t = 32 registers = lane t, 32 columns of the group's operand buffer; k interleaved
-        // inside every group of eight, the order the helper warp gives the activation tile
-        uint32_t regs[32];
-        if (grp.fast) {
+      // row t of the operand tile; chunk j goes to position j ^ (t & 7): one XOR on the shared-memory address
+      const uint32_t wrow = smem_u32(w_base + buf * W4_W_BYTES + row_off) ^ (static_cast<uint32_t>(t & 7) << 4);
+      if (grp.fast) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint4 w8 = grp.expand_interleaved<true>(words[j]);
-            regs[4 * j] = w8.x, regs[4 * j + 1] = w8.y, regs[4 * j + 2] = w8.z, regs[4 * j + 3] = w8.w;
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint4 w8 = grp.expand_interleaved<false>(words[j]);
-            regs[4 * j] = w8.x, regs[4 * j + 1] = w8.y, regs[4 * j + 2] = w8.z, regs[4 * j + 3] = w8.w;
-          }
+        for (int j = 0; j < 8; ++j) {
+          const uint4 w8 = grp.expand<true>(words[j]);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wrow ^ (j << 4)), "r"(w8.x), "r"(w8.y),
+                       "r"(w8.z), "r"(w8.w) : "memory");
         }
-        tc_fence_after();      // the buffer's last readers (MMAs) completed through w_empty
-        tmem_st32(tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + W4_A_TMEM_COL0 +
-                      (grp_id * W4_WBUFS + buf) * (W4_BK / 2), regs);
-        tc_wait_st();
-        tc_fence_before();
       } else {
-        // row t of the operand tile; chunk j goes to position j ^ (t & 7): one XOR on the shared-memory address
-        const uint32_t wrow = smem_u32(w_base + buf * W4_W_BYTES + row_off) ^ (static_cast<uint32_t>(t & 7) << 4);
-        if (grp.fast) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint4 w8 = grp.expand<true>(words[j]);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wrow ^ (j << 4)), "r"(w8.x), "r"(w8.y),
-                         "r"(w8.z), "r"(w8.w) : "memory");
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const uint4 w8 = grp.expand<false>(words[j]);
-            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wrow ^ (j << 4)), "r"(w8.x), "r"(w8.y),
-                         "r"(w8.z), "r"(w8.w) : "memory");
-          }
+        for (int j = 0; j < 8; ++j) {
+          const uint4 w8 = grp.expand<false>(words[j]);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(wrow ^ (j << 4)), "r"(w8.x), "r"(w8.y),
+                       "r"(w8.z), "r"(w8.w) : "memory");
         }
-        // make the generic-proxy writes visible to the tensor core (async proxy) before signalling
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       }
+      // make the generic-proxy writes visible to the tensor core (async proxy) before signalling
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
       if (lane == 0) mbar_arrive(&my_w_full[buf]);
       st += W4_GROUPS;
@@ -427,33 +387,6 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 #pragma unroll
       for (int i = 0; i < 16; ++i) partial[(c0 + i) * W4_BN + t] = acc[i];
     }
-  } else {
-    // ---------------- helper warp of a group: activation tiles into the weights' k order ----------------
-    if constexpr (ATMEM) {
-      const int grp_id = warp - W4_HELPER_WARP0;
-      uint64_t* my_w_full = w_full + grp_id * W4_WBUFS;
-      uint64_t* my_w_empty = w_empty + grp_id * W4_WBUFS;
-      int st = grp_id;
-      uint32_t in_ph = 0, buf = 0, w_ph = 0;
-      for (int i = grp_id; i < nkb; i += W4_GROUPS) {
-        // not ahead of the dequantisers: its arrival belongs to the same phase of w_full as theirs
-        if (!wait_or_abort(&my_w_empty[buf], w_ph ^ 1, abort_flag, 0x841)) break;
-        if (!wait_or_abort(&in_full[st], in_ph, abort_flag, 0x840)) break;
-        for (int ch = lane; ch < p.m_pad * 8; ch += 32) permute_chunk(reinterpret_cast<uint4*>(sX + st * p.x_bytes) + ch);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&my_w_full[buf]);
-        st += W4_GROUPS;
-        if (st >= in_stages) {
-          st -= in_stages;
-          in_ph ^= 1;
-        }
-        if (++buf == W4_WBUFS) {
-          buf = 0;
-          w_ph ^= 1;
-        }
-      }
-    }
   }
 
   // every CTA of the cluster has parked its partial tile
@@ -461,7 +394,7 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   cluster.sync();
 
-  if (warp >= 4 && warp < W4_HELPER_WARP0) {
+  if (warp >= 4) {
     const int t = (threadIdx.x - 128) & 127;
     const int grp_id = (threadIdx.x - 128) >> 7;
     const int n = n0 + t;
@@ -488,6 +421,313 @@ w4a16_gemm_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------------------------
+// Batches of up to 64 rows: the same four pipelines, but a round of a pipeline is TWO consecutive K steps (128 of K).
+// A dequantising warp issues about 350 instructions per 64-wide step of which only about 110 expand weights; the rest
+// is the step's bookkeeping (scale and zero point, addresses, barrier polls, fences, the arrive).  With two steps per
+// round that bookkeeping is paid once per 16 packed words: one scale / zero point when the quantisation group covers
+// both steps, one pair of barrier polls, one tcgen05.wait::st, one arrive, and the issuing thread wakes once for eight
+// MMAs.  The two operand buffers of a group (32 columns each, adjacent) then hold the two halves of one round, so a
+// group's dequantisers expand the first half of the next round in registers while the MMAs of the current one run and
+// store it once those are complete.
+// K steps of the CTA: round q covers steps 2q and 2q + 1; round q belongs to group q % 4; its input stage is
+// q % in_stages (in_stages is a multiple of four, counted in rounds).
+// ----------------------------------------------------------------------------------------------------------------
+constexpr int W4P_STAGE_RAW = 2 * W4_RAW_BYTES;       // packed words of a round: 16 rows x 128 columns, 8 KB
+
+// Eight consecutive k of one activation row (a 16-byte chunk, wherever the swizzle put it) into the order the
+// weights are expanded in: k = 0, 4, 1, 5, 2, 6, 3, 7.
+__device__ __forceinline__ void permute_chunk(uint4* px) {
+  const uint4 x = *px;
+  *px = make_uint4(__byte_perm(x.x, x.z, 0x5410), __byte_perm(x.x, x.z, 0x7632), __byte_perm(x.y, x.w, 0x5410),
+                   __byte_perm(x.y, x.w, 0x7632));
+}
+
+__global__ void __launch_bounds__(W4_THREADS, 1)
+w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX,
+                       const W4Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // layout: [X ring: two 64-wide tiles per stage][packed ring][barriers]; the front doubles as the fp32 partial tile
+  const int xs_bytes = 2 * p.x_bytes;
+  uint8_t* sX = smem;
+  uint8_t* sQ = sX + p.in_stages * xs_bytes;
+  uint64_t* in_full = reinterpret_cast<uint64_t*>(sQ + p.in_stages * W4P_STAGE_RAW);
+  uint64_t* in_empty = in_full + W4_MAX_IN;
+  uint64_t* w_full = in_empty + W4_MAX_IN;         // [group]
+  uint64_t* w_empty = w_full + W4_GROUPS;          // [group]
+  uint64_t* tfull = w_empty + W4_GROUPS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tfull + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  cgx::cluster_group cluster = cgx::this_cluster();
+  const int S = static_cast<int>(cluster.num_blocks());
+  const int rank = static_cast<int>(cluster.block_rank());
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * W4_BN;
+
+  // this CTA's K steps; a slice starts on an even step, so that rounds never straddle two CTAs
+  const int KB = p.k / W4_BK;
+  const int per = ((KB + S - 1) / S + 1) & ~1;
+  const int kb_begin = min(KB, rank * per);
+  const int kb_end = min(KB, kb_begin + per);
+  const int nkb = kb_end - kb_begin;
+  const int nrounds = (nkb + 1) / 2;
+  const int in_stages = p.in_stages;
+  const int spg = in_stages / W4_GROUPS;           // input stages per group
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < W4_MAX_IN; ++s) {
+      mbar_init(&in_full[s], 1);
+      mbar_init(&in_empty[s], 1);
+    }
+    for (int g = 0; g < W4_GROUPS; ++g) {
+      mbar_init(&w_full[g], 5);      // the four warps of the group and its helper warp
+      mbar_init(&w_empty[g], 1);
+    }
+    mbar_init(tfull, W4_GROUPS);     // one arrival per group, after its last MMA
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmX);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // columns [0, 4 m_pad): the groups' accumulators; [256, 512): the groups' operand buffers, 64 columns each
+
+  if (warp < W4_GROUPS) {
+    // ---------------- per group: TMA producer + MMA issuer (one thread) ----------------
+    if (lane == 0) {
+      const int grp_id = warp;
+      const int own = nrounds > grp_id ? (nrounds - grp_id + W4_GROUPS - 1) / W4_GROUPS : 0;   // rounds of this group
+      const uint32_t idesc = umma_idesc_f16(false, W4_BN, p.m_pad);
+      const uint32_t d_tmem = tmem_base + grp_id * p.m_pad;
+      const uint32_t a_tmem = tmem_base + 256 + grp_id * 64;
+      auto load = [&](int j) {           // own round j -> its stage (the caller has made sure the stage is free)
+        const int st = grp_id + W4_GROUPS * (j % spg);
+        const int kb = kb_begin + 2 * (grp_id + W4_GROUPS * j);
+        mbar_expect_tx(&in_full[st], W4P_STAGE_RAW + xs_bytes);
+        // the packed matrix is addressed as 16-bit elements: column 2*n, row k/8; steps past the end of K read zeros
+        tma_load_2d(sQ + st * W4P_STAGE_RAW, &tmQ, &in_full[st], 2 * n0, kb * (W4_BK / 8));
+        tma_load_2d(sQ + st * W4P_STAGE_RAW + W4_RAW_BYTES, &tmQ, &in_full[st], 2 * n0, (kb + 1) * (W4_BK / 8));
+        tma_load_2d(sX + st * xs_bytes, &tmX, &in_full[st], kb * W4_BK, 0);
+        tma_load_2d(sX + st * xs_bytes + p.x_bytes, &tmX, &in_full[st], (kb + 1) * W4_BK, 0);
+      };
+      const int pre = own < spg ? own : spg;
+      for (int j = 0; j < pre; ++j) load(j);
+      bool ok = true;
+      for (int j = 0; j < own && ok; ++j) {
+        // refill the stage of the previous own round first (its MMAs were issued a whole round ago)
+        if (j >= 1 && j - 1 + spg < own) {
+          const int pst = grp_id + W4_GROUPS * ((j - 1) % spg);
+          if (!wait_or_abort(&in_empty[pst], static_cast<uint32_t>((j - 1) / spg) & 1u, abort_flag, 0x900)) {
+            ok = false;
+            break;
+          }
+          load(j - 1 + spg);
+        }
+        const int st = grp_id + W4_GROUPS * (j % spg);
+        const int kb = kb_begin + 2 * (grp_id + W4_GROUPS * j);
+        const int halves = kb + 1 < kb_end ? 2 : 1;
+        if (!wait_or_abort(&w_full[grp_id], static_cast<uint32_t>(j) & 1u, abort_flag, 0x911)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int h = 0; h < halves; ++h) {
+          const uint64_t bdesc = umma_desc_sw128(smem_u32(sX + st * xs_bytes + h * p.x_bytes));
+#pragma unroll
+          for (int kk = 0; kk < W4_BK / 16; ++kk)
+            tc_mma_f16_a_tmem(d_tmem, a_tmem + 32 * h + 8 * kk, bdesc + 2 * kk, idesc, (j > 0 || h > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&w_empty[grp_id]);
+        tc_commit(&in_empty[st]);
+      }
+      // all of the group's MMAs (none, for a group without rounds) are complete when this arrives
+      if (ok && own > 0) tc_commit(tfull);
+      else mbar_arrive(tfull);
+    }
+  } else if (warp < W4_HELPER_WARP0) {
+    // ---------------- dequantise, then drain ----------------
+    const int t = (threadIdx.x - 128) & 127;        // output column n0 + t, TMEM lane t
+    const int grp_id = (threadIdx.x - 128) >> 7;    // owns rounds grp_id, grp_id + 4, ...
+    const int own = nrounds > grp_id ? (nrounds - grp_id + W4_GROUPS - 1) / W4_GROUPS : 0;
+    const int n = n0 + t;
+    const bool n_ok = n < p.n;
+    const __half* sp = p.scales + n;
+    const int32_t* zp = p.qzeros + (n >> 3);
+    const int zshift = (n & 7) * 4;
+    const int kpg = p.groupsize / W4_BK;            // K steps per quantisation group
+    const bool one_group = (kpg & 1) == 0;          // a round (an even step and its successor) lies in one group
+    const int last_group = p.k / p.groupsize - 1;
+    // scale and zero point of the round's two steps; those of the next own round are loaded while this one is expanded
+    auto fetch = [&](int j, __half (&sv)[2], uint32_t (&zv)[2]) {
+      const int kb = kb_begin + 2 * (grp_id + W4_GROUPS * j);
+      const int g0 = kb / kpg;
+      int g1 = (kb + 1) / kpg;
+      g1 = g1 > last_group ? last_group : g1;       // a second step past the end of K multiplies zeros
+      sv[0] = sv[1] = __ushort_as_half(0);
+      zv[0] = zv[1] = 0;
+      if (n_ok) {
+        sv[0] = __ldg(sp + static_cast<int64_t>(g0) * p.n);
+        zv[0] = static_cast<uint32_t>(__ldg(zp + static_cast<int64_t>(g0) * (p.n >> 3)));
+        if (!one_group) {
+          sv[1] = __ldg(sp + static_cast<int64_t>(g1) * p.n);
+          zv[1] = static_cast<uint32_t>(__ldg(zp + static_cast<int64_t>(g1) * (p.n >> 3)));
+        }
+      }
+    };
+    const uint32_t a_tmem = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + 256 + grp_id * 64;
+    auto expand_round = [&](const W4Group& grp, const uint32_t (&words)[8], uint32_t (&regs)[32]) {
+      if (grp.fast) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 w8 = grp.expand_interleaved<true>(words[i]);
+          regs[4 * i] = w8.x, regs[4 * i + 1] = w8.y, regs[4 * i + 2] = w8.z, regs[4 * i + 3] = w8.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const uint4 w8 = grp.expand_interleaved<false>(words[i]);
+          regs[4 * i] = w8.x, regs[4 * i + 1] = w8.y, regs[4 * i + 2] = w8.z, regs[4 * i + 3] = w8.w;
+        }
+      }
+    };
+    bool ok = true;
+    __half s_next[2];
+    uint32_t z_next[2];
+    s_next[0] = s_next[1] = __ushort_as_half(0);
+    z_next[0] = z_next[1] = 0;
+    if (own > 0) fetch(0, s_next, z_next);
+    int st = grp_id;
+    uint32_t in_ph = 0;
+    for (int j = 0; j < own; ++j) {
+      const int kb = kb_begin + 2 * (grp_id + W4_GROUPS * j);
+      const bool two = kb + 1 < kb_end;
+      W4Group grp_a, grp_b;
+      grp_a.set(s_next[0], (z_next[0] >> zshift) & 0xFu);
+      if (one_group) grp_b = grp_a;
+      else grp_b.set(s_next[1], (z_next[1] >> zshift) & 0xFu);
+      if (j + 1 < own) fetch(j + 1, s_next, z_next);
+      if (!wait_or_abort(&in_full[st], in_ph, abort_flag, 0x920)) {
+        ok = false;
+        break;
+      }
+      const uint32_t* q = reinterpret_cast<const uint32_t*>(sQ + st * W4P_STAGE_RAW) + t;
+      uint32_t words[8], regs[32];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) words[i] = q[i * W4_BN];
+      expand_round(grp_a, words, regs);            // in registers while the previous round's MMAs still run
+      if (two) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) words[i] = q[(8 + i) * W4_BN];
+      }
+      // the group's operand buffers are free once the MMAs of its previous round are complete
+      if (!wait_or_abort(&w_empty[grp_id], (static_cast<uint32_t>(j) & 1u) ^ 1u, abort_flag, 0x921)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      tmem_st32(a_tmem, regs);
+      if (two) {
+        expand_round(grp_b, words, regs);
+        tmem_st32(a_tmem + 32, regs);
+      }
+      tc_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&w_full[grp_id]);
+      st += W4_GROUPS;
+      if (st >= in_stages) {
+        st -= in_stages;
+        in_ph ^= 1;
+      }
+    }
+
+    // partial tile -> this CTA's shared memory as fp32 [m_pad][128] (column t contiguous across lanes);
+    // the four groups take 16-row chunks in turn and add the groups' accumulators in a fixed order
+    float* partial = reinterpret_cast<float*>(smem);
+    ok = wait_or_abort(tfull, 0, abort_flag, 0x930) && (*abort_flag == 0);
+    tc_fence_after();
+    const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    const int used = nrounds < W4_GROUPS ? nrounds : W4_GROUPS;
+    for (int c0 = grp_id * 16; c0 < p.m_pad; c0 += W4_GROUPS * 16) {
+      float acc[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) acc[i] = 0.0f;
+      if (ok) {
+        for (int a = 0; a < used; ++a) {
+          uint32_t raw[16];
+          tmem_ld16(taddr + a * p.m_pad + c0, raw);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[i] = (a == 0) ? __uint_as_float(raw[i]) : __fadd_rn(acc[i], __uint_as_float(raw[i]));
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; ++i) partial[(c0 + i) * W4_BN + t] = acc[i];
+    }
+  } else {
+    // ---------------- helper warp of a group: activation tiles into the weights' k order ----------------
+    const int grp_id = warp - W4_HELPER_WARP0;
+    int st = grp_id;
+    uint32_t in_ph = 0;
+    for (int q = grp_id, j = 0; q < nrounds; q += W4_GROUPS, ++j) {
+      // not ahead of the dequantisers: its arrival belongs to the same phase of w_full as theirs
+      if (!wait_or_abort(&w_empty[grp_id], (static_cast<uint32_t>(j) & 1u) ^ 1u, abort_flag, 0x941)) break;
+      if (!wait_or_abort(&in_full[st], in_ph, abort_flag, 0x940)) break;
+      for (int ch = lane; ch < 2 * p.m_pad * 8; ch += 32) permute_chunk(reinterpret_cast<uint4*>(sX + st * xs_bytes) + ch);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&w_full[grp_id]);
+      st += W4_GROUPS;
+      if (st >= in_stages) {
+        st -= in_stages;
+        in_ph ^= 1;
+      }
+    }
+  }
+
+  // every CTA of the cluster has parked its partial tile
+  tc_fence_before();
+  __syncthreads();
+  cluster.sync();
+
+  if (warp >= 4 && warp < W4_HELPER_WARP0) {
+    const int t = (threadIdx.x - 128) & 127;
+    const int grp_id = (threadIdx.x - 128) >> 7;
+    const int n = n0 + t;
+    if (n < p.n) {
+      for (int row = rank + grp_id * S; row < p.m; row += W4_GROUPS * S) {
+        // all remote loads in flight together, then the sum in rank order
+        float v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+          v[r] = 0.0f;
+          if (r < S) v[r] = cluster.map_shared_rank(reinterpret_cast<float*>(smem), r)[row * W4_BN + t];
+        }
+        float acc = v[0];
+#pragma unroll
+        for (int r = 1; r < 8; ++r)
+          if (r < S) acc = __fadd_rn(acc, v[r]);
+        p.c[static_cast<int64_t>(row) * p.ldc + n] = __float2half_rn(acc);
+      }
+    }
+  }
+  // nobody leaves while another CTA may still read its shared memory
+  cluster.sync();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
   }
 }
 
@@ -558,31 +798,34 @@ int w4a16_gemm_dispatch(const void* a, int64_t lda, const int32_t* qweight, cons
     p.groupsize = groupsize;
     p.x_bytes = p.m_pad * 128;
     const bool a_tmem = p.m_pad <= W4_ATMEM_MAX_M;
-    auto kern = a_tmem ? w4a16_gemm_kernel<true> : w4a16_gemm_kernel<false>;
+    auto kern = a_tmem ? w4a16_gemm_pair_kernel : w4a16_gemm_smem_kernel;
+    // a pipeline stage: one K step (shared-memory operand) or a round of two (tensor-memory operand)
     const int w_ring = a_tmem ? 0 : W4_WSTAGES * W4_W_BYTES;
-    int stages = (W4_SMEM_BUDGET - w_ring) / (W4_RAW_BYTES + p.x_bytes);
+    const int stage_bytes = (a_tmem ? 2 : 1) * (W4_RAW_BYTES + p.x_bytes);
+    int stages = (W4_SMEM_BUDGET - w_ring) / stage_bytes;
     const int steps = (KB + S - 1) / S;
-    if (stages > steps) stages = steps;
+    const int units = a_tmem ? (steps + 2) / 2 : steps;
+    if (stages > units) stages = units;
     if (stages > W4_MAX_IN) stages = W4_MAX_IN;
     // A multiple of the group count: the previous use of a stage then belongs to the same dequantising group,
     // which keeps every waiter within one phase of its barrier.
     p.in_stages = (stages + W4_GROUPS - 1) / W4_GROUPS * W4_GROUPS;
-    if ((W4_RAW_BYTES + p.x_bytes) * p.in_stages + w_ring > W4_SMEM_BUDGET) p.in_stages -= W4_GROUPS;
+    if (stage_bytes * p.in_stages + w_ring > W4_SMEM_BUDGET) p.in_stages -= W4_GROUPS;
     if (p.in_stages < W4_GROUPS) return FR_ERR_UNSUPPORTED;
     uint32_t cols = 32;
     while (cols < static_cast<uint32_t>(p.m_pad * W4_GROUPS)) cols *= 2;
     p.tmem_cols = a_tmem ? 512u : cols;
     // the partial tile (m_pad x 128 fp32) reuses the front of the rings
-    if (p.m_pad * W4_BN * 4 > w_ring + p.in_stages * (p.x_bytes + W4_RAW_BYTES)) return FR_ERR_UNSUPPORTED;
+    if (p.m_pad * W4_BN * 4 > w_ring + p.in_stages * stage_bytes) return FR_ERR_UNSUPPORTED;
     CUtensorMap tmX;
     rc = make_tmap_2d(&tmX, static_cast<const __half*>(a) + m0 * lda, static_cast<uint64_t>(mc),
                       static_cast<uint64_t>(k), static_cast<uint64_t>(lda), p.m_pad, 64, true);
     if (rc) return rc;
-    const int smem = w_ring + p.in_stages * (p.x_bytes + W4_RAW_BYTES) + 512 + 1024;
+    const int smem = w_ring + p.in_stages * stage_bytes + 512 + 1024;
     FR_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(n_tiles, S, 1);
-    cfg.blockDim = dim3(W4_THREADS);
+    cfg.blockDim = dim3(a_tmem ? W4_THREADS : W4_THREADS_SMEM);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
