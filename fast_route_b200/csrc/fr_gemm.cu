@@ -767,11 +767,14 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       const int64_t row = static_cast<int64_t>(m0) + q * 32 + lane;
       const bool row_ok = row < p.M;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
-      float tv[RKMAX];
+      // The sorted top list holds order-preserving integer images of the logits (fp32 bits with the sign folded,
+      // -0 taken as +0), so "stays ahead of the newcomer" is one unsigned compare; 0 is below every image, -inf
+      // included, and marks an empty slot.
+      uint32_t tv[RKMAX];
       int tc[RKMAX];
 #pragma unroll
       for (int j = 0; j < RKMAX; ++j) {
-        tv[j] = -INFINITY;
+        tv[j] = 0u;
         tc[j] = 0x7fffffff;
       }
       float run_max = -INFINITY, run_sum = 0.0f;
@@ -806,20 +809,21 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
                   run_sum = run_sum * __expf(run_max - nm) + __expf(x - nm);
                   run_max = nm;
                 }
-                // Insert into the sorted top list.  An entry stays ahead of the newcomer if it is larger, or equal
-                // with a lower expert id (columns arrive in ascending order).  keep[j] is monotone in j; slot j
-                // keeps its entry, takes the newcomer (first slot that does not keep), or takes slot j-1's entry.
-                // All eight decisions are independent: no carry chain through the list.
+                // Insert into the sorted top list.  An entry stays ahead of the newcomer if it is larger, or equal:
+                // columns arrive in ascending order, so an equal entry has the lower expert id.  keep[j] is monotone
+                // in j; slot j keeps its entry, takes the newcomer (first slot that does not keep), or takes slot
+                // j-1's entry.  All eight decisions are independent: no carry chain through the list.
+                const uint32_t xb = __float_as_uint(x + 0.0f);                    // -0 -> +0
+                const uint32_t xk = xb ^ ((xb & 0x80000000u) ? 0xFFFFFFFFu : 0x80000000u);
                 bool keep[RKMAX];
 #pragma unroll
-                for (int j = 0; j < RKMAX; ++j)   // bitwise on purpose: no short-circuit branches (empty slots: -inf, INT_MAX)
-                  keep[j] = static_cast<bool>(static_cast<int>(tv[j] > x) | (static_cast<int>(tv[j] == x) & static_cast<int>(tc[j] < c)));
+                for (int j = 0; j < RKMAX; ++j) keep[j] = tv[j] >= xk;
 #pragma unroll
                 for (int j = RKMAX - 1; j >= 1; --j) {
-                  tv[j] = keep[j] ? tv[j] : (keep[j - 1] ? x : tv[j - 1]);
+                  tv[j] = keep[j] ? tv[j] : (keep[j - 1] ? xk : tv[j - 1]);
                   tc[j] = keep[j] ? tc[j] : (keep[j - 1] ? c : tc[j - 1]);
                 }
-                tv[0] = keep[0] ? tv[0] : x;
+                tv[0] = keep[0] ? tv[0] : xk;
                 tc[0] = keep[0] ? tc[0] : c;
               }
             }
@@ -829,15 +833,19 @@ router_gemm_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       if (p.do_topk && row_ok) {
         float e[RKMAX];
         float s = 0.0f;
+        auto value_of = [](uint32_t key) {        // back from the integer image
+          return __uint_as_float(key ^ ((key & 0x80000000u) ? 0x80000000u : 0xFFFFFFFFu));
+        };
+        const float top = value_of(tv[0]);
 #pragma unroll
         for (int j = 0; j < RKMAX; ++j) {
           e[j] = 0.0f;
           if (j < p.topk) {
-            e[j] = exp_recipe(__fsub_rn(tv[j], tv[0]));
+            e[j] = exp_recipe(__fsub_rn(value_of(tv[j]), top));
             s = (j == 0) ? e[0] : __fadd_rn(s, e[j]);
           }
         }
-        if (!p.renormalize) s = run_sum * __expf(run_max - tv[0]);
+        if (!p.renormalize) s = run_sum * __expf(run_max - top);
 #pragma unroll
         for (int j = 0; j < RKMAX; ++j) {
           if (j < p.topk) {
