@@ -16,17 +16,17 @@
 //              words of a step into 64 fp16 weights.
 // Two kernels share this frame:
 //   w4a16_gemm_pair_kernel (up to 64 activation rows): the weights go from registers straight into lane t of a
-//              tensor-memory buffer (tcgen05.st) and the MMA reads its A operand there; a round of a group is two
+//              tensor-memory buffer (tcgen05.st) and the MMA reads its A operand there; a group works on pairs of
 //              consecutive K steps; the eight weights of a packed word come out with k interleaved (0, 4, 1, 5, 2, 6,
 //              3, 7: one shift and four mask-or operations per word instead of four byte permutes) and a helper warp
 //              per group (warps 20..23) gives the activation tile the same order in shared memory before the MMA
 //              reads it (a sum over k does not care about the order).
 //   w4a16_gemm_smem_kernel (65 to 128 rows, where the accumulators need the tensor-memory columns): the weights go
-//              into row t of a K-major, 128-byte-swizzled shared-memory tile, natural k order, one K step per round.
+//              into row t of a K-major, 128-byte-swizzled shared-memory tile, natural k order, one K step at a time.
 // A thread can issue a tcgen05.mma only every hundred cycles or so, whatever its shape, so one issuing thread per
 // CTA was the bottleneck; four pipelines that never wait for one another hide it.  The dequantising warps drain the
 // four accumulators at the end; warp 1 also allocates and frees TMEM.
-// At these sizes the kernels are bound by instruction issue, most of it the bookkeeping of a round (scale and zero
+// At these sizes the kernels are bound by instruction issue, most of it the bookkeeping of a pipeline turn (scale and zero
 // point, addresses, barrier polls, fences, the arrive) rather than the expansion itself, not by HBM or the tensor pipe.
 // Split-K runs as a thread-block cluster along K (1, 2, 4 or 8 CTAs): every CTA parks its fp32 partial tile in its
 // own shared memory, and after a cluster barrier CTA r sums rows r, r+S, ... over the ranks in rank order through
@@ -158,7 +158,7 @@ struct W4Group {
 };
 
 // Batches of more than 64 rows (the accumulators then need the tensor-memory columns): the dequantised operand goes
-// through shared memory, one K step per round, weights in natural k order.
+// through shared memory, one K step at a time, weights in natural k order.
 __global__ void __launch_bounds__(W4_THREADS_SMEM, 1)
 w4a16_gemm_smem_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmX, const W4Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -425,18 +425,18 @@ w4a16_gemm_smem_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
 }
 
 // ----------------------------------------------------------------------------------------------------------------
-// Batches of up to 64 rows: the same four pipelines, but a round of a pipeline is TWO consecutive K steps (128 of K).
+// Batches of up to 64 rows: the same four pipelines, but a pipeline takes its K steps in PAIRS (128 of K at a time).
 // A dequantising warp issues about 350 instructions per 64-wide step of which only about 110 expand weights; the rest
 // is the step's bookkeeping (scale and zero point, addresses, barrier polls, fences, the arrive).  With two steps per
-// round that bookkeeping is paid once per 16 packed words: one scale / zero point when the quantisation group covers
+// turn that bookkeeping is paid once per 16 packed words: one scale / zero point when the quantisation group covers
 // both steps, one pair of barrier polls, one tcgen05.wait::st, one arrive, and the issuing thread wakes once for eight
-// MMAs.  The two operand buffers of a group (32 columns each, adjacent) then hold the two halves of one round, so a
-// group's dequantisers expand the first half of the next round in registers while the MMAs of the current one run and
+// MMAs.  The two operand buffers of a group (32 columns each, adjacent) then hold the two halves of one pair, so a
+// group's dequantisers expand the first half of the next pair in registers while the MMAs of the current one run and
 // store it once those are complete.
-// K steps of the CTA: round q covers steps 2q and 2q + 1; round q belongs to group q % 4; its input stage is
-// q % in_stages (in_stages is a multiple of four, counted in rounds).
+// K steps of the CTA: pair q covers steps 2q and 2q + 1; pair q belongs to group q % 4; its input stage is
+// q % in_stages (in_stages is a multiple of four, counted in pairs).
 // ----------------------------------------------------------------------------------------------------------------
-constexpr int W4P_STAGE_RAW = 2 * W4_RAW_BYTES;       // packed words of a round: 16 rows x 128 columns, 8 KB
+constexpr int W4P_STAGE_RAW = 2 * W4_RAW_BYTES;       // packed words of a pair: 16 rows x 128 columns, 8 KB
 
 // Eight consecutive k of one activation row (a 16-byte chunk, wherever the swizzle put it) into the order the
 // weights are expanded in: k = 0, 4, 1, 5, 2, 6, 3, 7.
@@ -468,13 +468,13 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * W4_BN;
 
-  // this CTA's K steps; a slice starts on an even step, so that rounds never straddle two CTAs
+  // this CTA's K steps; a slice starts on an even step, so that pairs never straddle two CTAs
   const int KB = p.k / W4_BK;
   const int per = ((KB + S - 1) / S + 1) & ~1;
   const int kb_begin = min(KB, rank * per);
   const int kb_end = min(KB, kb_begin + per);
   const int nkb = kb_end - kb_begin;
-  const int nrounds = (nkb + 1) / 2;
+  const int npairs = (nkb + 1) / 2;
   const int in_stages = p.in_stages;
   const int spg = in_stages / W4_GROUPS;           // input stages per group
 
@@ -508,11 +508,11 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     // ---------------- per group: TMA producer + MMA issuer (one thread) ----------------
     if (lane == 0) {
       const int grp_id = warp;
-      const int own = nrounds > grp_id ? (nrounds - grp_id + W4_GROUPS - 1) / W4_GROUPS : 0;   // rounds of this group
+      const int own = npairs > grp_id ? (npairs - grp_id + W4_GROUPS - 1) / W4_GROUPS : 0;   // pairs of this group
       const uint32_t idesc = umma_idesc_f16(false, W4_BN, p.m_pad);
       const uint32_t d_tmem = tmem_base + grp_id * p.m_pad;
       const uint32_t a_tmem = tmem_base + 256 + grp_id * 64;
-      auto load = [&](int j) {           // own round j -> its stage (the caller has made sure the stage is free)
+      auto load = [&](int j) {           // own pair j -> its stage (the caller has made sure the stage is free)
         const int st = grp_id + W4_GROUPS * (j % spg);
         const int kb = kb_begin + 2 * (grp_id + W4_GROUPS * j);
         mbar_expect_tx(&in_full[st], W4P_STAGE_RAW + xs_bytes);
@@ -526,7 +526,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       for (int j = 0; j < pre; ++j) load(j);
       bool ok = true;
       for (int j = 0; j < own && ok; ++j) {
-        // refill the stage of the previous own round first (its MMAs were issued a whole round ago)
+        // refill the stage of the previous own pair first (its MMAs were issued a whole pair ago)
         if (j >= 1 && j - 1 + spg < own) {
           const int pst = grp_id + W4_GROUPS * ((j - 1) % spg);
           if (!wait_or_abort(&in_empty[pst], static_cast<uint32_t>((j - 1) / spg) & 1u, abort_flag, 0x900)) {
@@ -552,24 +552,24 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tc_commit(&w_empty[grp_id]);
         tc_commit(&in_empty[st]);
       }
-      // all of the group's MMAs (none, for a group without rounds) are complete when this arrives
+      // all of the group's MMAs (none, for a group without pairs) are complete when this arrives
       if (ok && own > 0) tc_commit(tfull);
       else mbar_arrive(tfull);
     }
   } else if (warp < W4_HELPER_WARP0) {
     // ---------------- dequantise, then drain ----------------
     const int t = (threadIdx.x - 128) & 127;        // output column n0 + t, TMEM lane t
-    const int grp_id = (threadIdx.x - 128) >> 7;    // owns rounds grp_id, grp_id + 4, ...
-    const int own = nrounds > grp_id ? (nrounds - grp_id + W4_GROUPS - 1) / W4_GROUPS : 0;
+    const int grp_id = (threadIdx.x - 128) >> 7;    // owns pairs grp_id, grp_id + 4, ...
+    const int own = npairs > grp_id ? (npairs - grp_id + W4_GROUPS - 1) / W4_GROUPS : 0;
     const int n = n0 + t;
     const bool n_ok = n < p.n;
     const __half* sp = p.scales + n;
     const int32_t* zp = p.qzeros + (n >> 3);
     const int zshift = (n & 7) * 4;
     const int kpg = p.groupsize / W4_BK;            // K steps per quantisation group
-    const bool one_group = (kpg & 1) == 0;          // a round (an even step and its successor) lies in one group
+    const bool one_group = (kpg & 1) == 0;          // a pair (an even step and its successor) lies in one group
     const int last_group = p.k / p.groupsize - 1;
-    // scale and zero point of the round's two steps; those of the next own round are loaded while this one is expanded
+    // scale and zero point of the pair's two steps; those of the next own pair are loaded while this one is expanded
     auto fetch = [&](int j, __half (&sv)[2], uint32_t (&zv)[2]) {
       const int kb = kb_begin + 2 * (grp_id + W4_GROUPS * j);
       const int g0 = kb / kpg;
@@ -587,7 +587,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
     };
     const uint32_t a_tmem = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + 256 + grp_id * 64;
-    auto expand_round = [&](const W4Group& grp, const uint32_t (&words)[8], uint32_t (&regs)[32]) {
+    auto expand_step = [&](const W4Group& grp, const uint32_t (&words)[8], uint32_t (&regs)[32]) {
       if (grp.fast) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -626,12 +626,12 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       uint32_t words[8], regs[32];
 #pragma unroll
       for (int i = 0; i < 8; ++i) words[i] = q[i * W4_BN];
-      expand_round(grp_a, words, regs);            // in registers while the previous round's MMAs still run
+      expand_step(grp_a, words, regs);            // in registers while the previous pair's MMAs still run
       if (two) {
 #pragma unroll
         for (int i = 0; i < 8; ++i) words[i] = q[(8 + i) * W4_BN];
       }
-      // the group's operand buffers are free once the MMAs of its previous round are complete
+      // the group's operand buffers are free once the MMAs of its previous pair are complete
       if (!wait_or_abort(&w_empty[grp_id], (static_cast<uint32_t>(j) & 1u) ^ 1u, abort_flag, 0x921)) {
         ok = false;
         break;
@@ -639,7 +639,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tc_fence_after();
       tmem_st32(a_tmem, regs);
       if (two) {
-        expand_round(grp_b, words, regs);
+        expand_step(grp_b, words, regs);
         tmem_st32(a_tmem + 32, regs);
       }
       tc_wait_st();
@@ -659,7 +659,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     ok = wait_or_abort(tfull, 0, abort_flag, 0x930) && (*abort_flag == 0);
     tc_fence_after();
     const uint32_t taddr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-    const int used = nrounds < W4_GROUPS ? nrounds : W4_GROUPS;
+    const int used = npairs < W4_GROUPS ? npairs : W4_GROUPS;
     for (int c0 = grp_id * 16; c0 < p.m_pad; c0 += W4_GROUPS * 16) {
       float acc[16];
 #pragma unroll
@@ -681,7 +681,7 @@ w4a16_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     const int grp_id = warp - W4_HELPER_WARP0;
     int st = grp_id;
     uint32_t in_ph = 0;
-    for (int q = grp_id, j = 0; q < nrounds; q += W4_GROUPS, ++j) {
+    for (int q = grp_id, j = 0; q < npairs; q += W4_GROUPS, ++j) {
       // not ahead of the dequantisers: its arrival belongs to the same phase of w_full as theirs
       if (!wait_or_abort(&w_empty[grp_id], (static_cast<uint32_t>(j) & 1u) ^ 1u, abort_flag, 0x941)) break;
       if (!wait_or_abort(&in_full[st], in_ph, abort_flag, 0x940)) break;
@@ -799,7 +799,7 @@ int w4a16_gemm_dispatch(const void* a, int64_t lda, const int32_t* qweight, cons
     p.x_bytes = p.m_pad * 128;
     const bool a_tmem = p.m_pad <= W4_ATMEM_MAX_M;
     auto kern = a_tmem ? w4a16_gemm_pair_kernel : w4a16_gemm_smem_kernel;
-    // a pipeline stage: one K step (shared-memory operand) or a round of two (tensor-memory operand)
+    // a pipeline stage: one K step (shared-memory operand) or a pair of them (tensor-memory operand)
     const int w_ring = a_tmem ? 0 : W4_WSTAGES * W4_W_BYTES;
     const int stage_bytes = (a_tmem ? 2 : 1) * (W4_RAW_BYTES + p.x_bytes);
     int stages = (W4_SMEM_BUDGET - w_ring) / stage_bytes;
