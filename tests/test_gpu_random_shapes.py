@@ -54,9 +54,9 @@ def test_layer_random_shapes(dev, seed):
 
 def test_w4a16_random_shapes(dev):
     rnd = random.Random(7)
-    for it in range(40):
-        m = rnd.choice([1, 2, 5, 16, 17, 33, 100, 128, 129, 200, 300])
-        gs = rnd.choice([64, 128, 256])
+    for it in range(60):
+        m = rnd.choice([1, 2, 5, 16, 17, 33, 48, 64, 65, 100, 128, 129, 200, 300])   # 64 / 65: the two GEMM kernels
+        gs = rnd.choice([64, 128, 192, 256])       # 64 and 192: a pair of K steps spans two quantisation groups
         k = gs * rnd.choice([1, 2, 3, 4, 8, 16])
         n = 8 * rnd.choice([1, 3, 8, 16, 17, 33, 64, 100, 129])
         g = torch.Generator().manual_seed(it)
